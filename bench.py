@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: radix sort of uint32 keys (and scan / reduce / histogram
+beside it) on 1..8 B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+N = 1: one step = one ascending RadixSort of 2^26 uint32 keys (i.i.d. uniform, seeded).
+N > 1 (under torchrun, one rank per GPU): one step = one sample sort of N * 2^26 keys,
+2^26 per GPU (weak scaling): sampled splitters, stable partition, NCCL all-to-all of the
+buckets, local radix sort.
+`--impl reference` times the CPU restatement of the reference's CPUAccelerator sort on the
+host cores (the reference is C#; no .NET toolchain exists on these machines).
+
+Prints ONE JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+KEYS_PER_GPU = 1 << 26
+SORT_BYTES_PER_KEY = 36          # 4-byte keys: one histogram read + 4 x (read + write)
+SEED = 2
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.lines: list[str] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+# ------------------------------------------------------------------------------------------
+def cpu_reference_sort(sample_keys, cores: int, repeats: int = 1):
+    """Times the literal two-kernel 2-bit CPU sort spread over `cores` threads; returns
+    (Gkeys/s, seconds per run)."""
+    import numpy as np
+    from oracle import cpu_oracle as oracle
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        out = oracle.radix_sort_literal_mt(sample_keys, False, 16 * cores, cores)
+        dt = time.perf_counter() - t0
+        best = dt if best is None or dt < best else best
+    assert np.all(out[1:] >= out[:-1])
+    return sample_keys.size / best / 1e9, best
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from ilgpu_b200 import synthetic
+    cores = host_cores()
+    sample = 1 << 24
+    keys = synthetic.uniform_uint32(sample * 2, SEED)
+    times = []
+    for step in range(args.warmup + args.steps):
+        part = keys[(step % 2) * sample:(step % 2 + 1) * sample]
+        _, dt = cpu_reference_sort(part, cores)
+        if step >= args.warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    value = sample / sec / 1e9
+    line = {
+        "impl": "reference", "metric": "radix_sort_gkeys_per_s", "value": value, "unit": "Gkeys/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+        "config": {"workload": "RadixSort ascending, 2^26 uint32 keys i.i.d. uniform (seeded)",
+                   "keys_per_gpu": KEYS_PER_GPU, "sample_keys_per_step": sample},
+        "cpu_baseline": {"value": value, "unit": "Gkeys/s", "cores": cores, "kind": "port",
+                         "sample": "2^24-key slice of the 2^26-key workload per step; C restatement of "
+                                   "CPURadixSortKernel1/2 (2 bits per pass), groups spread over all host threads"},
+        "e2e": {"value": value, "unit": "Gkeys/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+def time_region(fn, steps: int, stream) -> float:
+    """Milliseconds per step of `fn(i)` over `steps` calls, by CUDA events on `stream`."""
+    import torch
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record(stream)
+    for i in range(steps):
+        fn(i)
+    end.record(stream)
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / steps
+
+
+def secondary_metrics(acc, peak_gbs: float) -> dict:
+    """Scan / reduce / histogram throughput on their own configurations (1 GPU, resident
+    inputs larger than L2, CUDA events)."""
+    import torch
+    import ilgpu_b200 as ib
+    from ilgpu_b200 import synthetic
+    stream = torch.cuda.current_stream()
+    out = {}
+    Ops = ib.ScanReduceOperations
+
+    def gbs(nbytes, ms):
+        v = nbytes / (ms * 1e-3) / 1e9
+        return {"GB/s": round(v, 1), "frac_of_measured_hbm": round(v / peak_gbs, 4), "ms": round(ms, 4)}
+
+    # float32 inclusive scan + sum reduce over 2^30 values (8 B and 4 B per element)
+    n = 1 << 30
+    x = synthetic.uniform_float32_device(n, 5, "cuda")
+    y = torch.empty_like(x)
+    temp = acc.Allocate1D(acc.ComputeScanTempStorageSize(torch.float32, n), torch.int32)
+    scan = acc.CreateScan(Ops.AddFloat, ib.ScanKind.Inclusive)
+    for _ in range(3):
+        scan(None, x, y, temp)
+    out["scan_f32_inclusive_2^30"] = gbs(8 * n, time_region(lambda i: scan(None, x, y, temp), 5, stream))
+    red = acc.CreateReduction(Ops.AddFloat)
+    cell = acc.Allocate1D(1, torch.float32)
+    for _ in range(3):
+        red(None, x, cell)
+    out["reduce_f32_sum_2^30"] = gbs(4 * n, time_region(lambda i: red(None, x, cell), 5, stream))
+    del x, y, temp
+    # int32 reduce + exclusive scan over 2^24 values, rotating over 8 buffers (64 MiB each)
+    n = 1 << 24
+    bufs = [synthetic.uniform_int32_device(n, 1, "cuda", start=i * n) for i in range(8)]
+    outs = [torch.empty_like(b) for b in bufs]
+    temp = acc.Allocate1D(acc.ComputeScanTempStorageSize(torch.int32, n), torch.int32)
+    scan = acc.CreateScan(Ops.AddInt32, ib.ScanKind.Exclusive)
+    red = acc.CreateReduction(Ops.AddInt32)
+    cell = acc.Allocate1D(1, torch.int32)
+    for i in range(8):
+        scan(None, bufs[i], outs[i], temp); red(None, bufs[i], cell)
+    out["scan_i32_exclusive_2^24"] = gbs(8 * n, time_region(lambda i: scan(None, bufs[i % 8], outs[i % 8], temp), 16, stream))
+    out["reduce_i32_sum_2^24"] = gbs(4 * n, time_region(lambda i: red(None, bufs[i % 8], cell), 16, stream))
+    del bufs, outs
+    # histogram of 2^28 float32 N(0,1) into 256 int32 bins
+    n = 1 << 28
+    f = synthetic.normal_float32_device(n, 3, "cuda")
+    bins = torch.zeros(256, dtype=torch.int32, device="cuda")
+    ovf = torch.zeros(1, dtype=torch.int32, device="cuda")
+    hist = acc.CreateHistogram(ib.EqualWidthClampLocator(-4.0, 4.0))
+    for _ in range(3):
+        hist(None, f, bins, ovf)
+    out["histogram_f32_256bins_2^28"] = gbs(4 * n, time_region(lambda i: hist(None, f, bins, ovf), 5, stream))
+    return out
+
+
+def run_native(args) -> None:
+    import numpy as np
+    import torch
+    import ilgpu_b200 as ib
+    from ilgpu_b200 import synthetic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    acc = ib.Accelerator(local_rank)
+    stream = torch.cuda.current_stream()
+    peak_gbs, peak_kind = measured_peaks()
+    n = KEYS_PER_GPU
+    steps, warmup = args.steps, args.warmup
+    op = ib.RadixSortOperations.AscendingUInt32
+
+    # One fresh unsorted buffer per step (the sort is in place); 256 MiB each, larger than L2.
+    nbuf = steps + warmup
+    pristine = synthetic.uniform_uint32_device(n, SEED, "cuda", start=rank * n)
+    checksum_in = int(pristine.view(torch.int32).to(torch.int64).sum().item())
+
+    if world == 1:
+        bufs = [pristine.clone() for _ in range(nbuf)]
+        temp = acc.Allocate1D(acc.ComputeRadixSortTempStorageSize(op, n), torch.int32)
+        sort = acc.CreateRadixSort(op)
+
+        def step_fn(i):
+            sort(None, bufs[i], temp)
+        launches_per_step = 7   # histogram, offsets, 4 digit passes, copy-back (exits at once)
+        result_of = lambda i: bufs[i]
+    else:
+        from ilgpu_b200.multi_gpu import ShardedAlgorithms
+        sharded = ShardedAlgorithms(acc, dist.group.WORLD)
+        bufs = [pristine.clone() for _ in range(nbuf)]
+        results = [None] * nbuf
+
+        def step_fn(i):
+            results[i] = sharded.SortKeys(bufs[i], op)
+        launches_per_step = sharded.sort_launches_per_step(op)
+        result_of = lambda i: results[i][0]
+
+    for i in range(warmup):
+        step_fn(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(warmup, warmup + steps):
+        step_fn(i)
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    ms_total = ev0.elapsed_time(ev1)
+    if dist is not None:
+        t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        ms_total = float(t.item())
+    clocks = sampler.stop()
+    ms_per_step = ms_total / steps
+    value = world * n / (ms_per_step * 1e-3) / 1e9
+
+    # sanity of the timed work (the parity tests proper live in tests/)
+    last = result_of(warmup + steps - 1)
+    li = last.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    assert bool((li[1:] >= li[:-1]).all()), "result is not sorted"
+    if world == 1:
+        assert int(last.view(torch.int32).to(torch.int64).sum().item()) == checksum_in, "keys were lost"
+    del li
+
+    # end to end through the public API with host buffers: H2D of the keys, sort, D2H of the result
+    e2e_steps = max(1, min(steps, 8))
+    host_in = torch.empty(n, dtype=torch.uint32).pin_memory()
+    host_in.copy_(pristine.cpu())
+    host_out = torch.empty(n, dtype=torch.uint32).pin_memory()
+    dev = bufs[0]
+
+    def e2e_fn(i):
+        dev.copy_(host_in, non_blocking=True)
+        if world == 1:
+            sort(None, dev, temp)
+            host_out.copy_(dev, non_blocking=True)
+        else:
+            out, count = sharded.SortKeys(dev, op)
+            host_out[: min(n, out.numel())].copy_(out[: min(n, out.numel())], non_blocking=True)
+    for i in range(2):
+        e2e_fn(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    e2e_ms = time_region(e2e_fn, e2e_steps, stream)
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * n / (e2e_ms * 1e-3) / 1e9
+
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    achieved = SORT_BYTES_PER_KEY * n / (ms_per_step * 1e-3) / 1e9   # per GPU
+    line = {
+        "metric": "radix_sort_gkeys_per_s", "value": value, "unit": "Gkeys/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+        "config": {
+            "workload": "RadixSort ascending, 2^26 uint32 keys per GPU, i.i.d. uniform over the full range (seeded), "
+                        "4 digit passes of 8 bits" + ("" if world == 1 else "; sample sort across GPUs with NCCL all-to-all"),
+            "keys_per_gpu": n, "total_keys": world * n,
+            "l2": "inputs larger than L2: 256 MiB per step, a fresh unsorted buffer each step",
+        },
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+            "traffic": None, "peak_kind": peak_kind,
+            "kernel": "whole sort call (digit histograms + 4 onesweep passes); 36 B/key algorithmic",
+        },
+        "e2e": {"value": e2e_value, "unit": "Gkeys/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4 * n,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": launches_per_step * steps,
+        "clocks": clocks,
+    }
+    if world == 1:
+        if not args.no_secondary:
+            del bufs
+            torch.cuda.empty_cache()
+            line["secondary"] = secondary_metrics(acc, peak_gbs)
+        cores = host_cores()
+        sample = 1 << 24
+        cpu_value, cpu_sec = cpu_reference_sort(pristine[:sample].cpu().numpy(), cores)
+        line["cpu_baseline"] = {
+            "value": cpu_value, "unit": "Gkeys/s", "cores": cores, "kind": "port",
+            "sample": f"first 2^24 keys of the workload, one run of {cpu_sec:.2f} s; C restatement of the reference's "
+                      "CPURadixSortKernel1/2 (2 bits per pass), groups spread over all host threads",
+        }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-secondary", action="store_true", help="skip the scan / reduce / histogram figures")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,105 @@
+// Library-wide helpers, status reporting, and the fill / iota kernels that sit on the
+// edges of the path (InitializeExtensions.cs, SequenceExtensions.cs).
+#include "common.cuh"
+
+namespace b200alg {
+
+thread_local int g_last_cuda_error = 0;
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cached[dev] = v;
+    }
+    return cached[dev];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) fill_kernel(T *view, int64_t stride, int64_t n, T value) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) view[i * stride] = value;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) sequence_kernel(T *view, int64_t n, T start, T step_value) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step)
+        view[i] = (T)(start + (T)i * step_value);
+}
+
+static int grid_for(int64_t n) {
+    int64_t want = ceil_div(n, 256 * 4);
+    int64_t cap = (int64_t)sm_count() * 8;
+    return (int)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+}  // namespace b200alg
+
+using namespace b200alg;
+
+extern "C" int b200alg_version(void) { return B200ALG_VERSION; }
+
+extern "C" const char *b200alg_status_string(int status) {
+    switch (status) {
+    case B200ALG_OK: return "success";
+    case B200ALG_INVALID_ARGUMENT: return "invalid argument";
+    case B200ALG_UNSUPPORTED: return "unsupported element type, operation or value size";
+    case B200ALG_TEMP_TOO_SMALL: return "temporary storage too small";
+    case B200ALG_CUDA_ERROR: return "CUDA error (see b200alg_last_cuda_error)";
+    case B200ALG_WAIT_LIMIT: return "a device-side wait exceeded its iteration limit";
+    case B200ALG_MISALIGNED: return "pointer not aligned";
+    case B200ALG_TOO_LARGE: return "more than INT32_MAX elements";
+    }
+    return "unknown status";
+}
+
+extern "C" int b200alg_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int b200alg_initialize(void *stream, void *view, int64_t stride, int64_t n, int elem_bytes, const void *value) {
+    if (n < 0 || stride < 1 || (n > 0 && !view) || !value) return B200ALG_INVALID_ARGUMENT;
+    if (n == 0) return B200ALG_OK;
+    if ((uintptr_t)view % elem_bytes) return B200ALG_MISALIGNED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int g = grid_for(n);
+    switch (elem_bytes) {
+    case 1: fill_kernel<uint8_t><<<g, 256, 0, s>>>((uint8_t *)view, stride, n, *(const uint8_t *)value); break;
+    case 2: fill_kernel<uint16_t><<<g, 256, 0, s>>>((uint16_t *)view, stride, n, *(const uint16_t *)value); break;
+    case 4: fill_kernel<uint32_t><<<g, 256, 0, s>>>((uint32_t *)view, stride, n, *(const uint32_t *)value); break;
+    case 8: fill_kernel<uint64_t><<<g, 256, 0, s>>>((uint64_t *)view, stride, n, *(const uint64_t *)value); break;
+    case 16: fill_kernel<uint4><<<g, 256, 0, s>>>((uint4 *)view, stride, n, *(const uint4 *)value); break;
+    default: return B200ALG_UNSUPPORTED;
+    }
+    B200ALG_LAUNCH_CHECK();
+    return B200ALG_OK;
+}
+
+extern "C" int b200alg_sequence(void *stream, void *view, int64_t n, int dtype, int64_t start, int64_t step) {
+    if (n < 0 || (n > 0 && !view)) return B200ALG_INVALID_ARGUMENT;
+    if (n == 0) return B200ALG_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int g = grid_for(n);
+    switch (dtype) {
+    case B200ALG_I32: case B200ALG_U32:
+        if ((uintptr_t)view % 4) return B200ALG_MISALIGNED;
+        sequence_kernel<uint32_t><<<g, 256, 0, s>>>((uint32_t *)view, n, (uint32_t)start, (uint32_t)step); break;
+    case B200ALG_I64: case B200ALG_U64:
+        if ((uintptr_t)view % 8) return B200ALG_MISALIGNED;
+        sequence_kernel<uint64_t><<<g, 256, 0, s>>>((uint64_t *)view, n, (uint64_t)start, (uint64_t)step); break;
+    default: return B200ALG_UNSUPPORTED;
+    }
+    B200ALG_LAUNCH_CHECK();
+    return B200ALG_OK;
+}
+
+extern "C" int b200alg_device_status(void *stream, const void *temp) {
+    if (!temp) return B200ALG_INVALID_ARGUMENT;
+    unsigned int flag = 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    B200ALG_CUDA_TRY(cudaMemcpyAsync(&flag, temp, sizeof(flag), cudaMemcpyDeviceToHost, s));
+    B200ALG_CUDA_TRY(cudaStreamSynchronize(s));
+    return flag ? B200ALG_WAIT_LIMIT : B200ALG_OK;
+}

@@ -1,0 +1,707 @@
+// Radix sort: onesweep-style least-significant-digit sort with 8-bit digits.
+//
+//   1. one pass over the keys builds the histograms of ALL digit positions,
+//   2. a one-block kernel turns them into global digit offsets and finds digit positions
+//      on which every key agrees (those passes are skipped),
+//   3. one kernel per remaining digit position: a tile of keys is ranked in shared memory
+//      (warp match / ballot), the tile's digit counts are chained to the previous tiles'
+//      with decoupled look-back, and the tile is scattered to its final place for that
+//      digit - each key is read once and written once per pass.
+//
+// Replaces RadixSortKernel1 / RadixSortKernel2 and the host loop around them
+// (RadixSortExtensions.cs:660-738, :852-912, :1276-1334: 2 bits per pass, 4 launches per
+// pass) and, for pairs, the AoS gather / sort / scatter of :1047-1073 (values are carried
+// structure-of-arrays here).  Every pass is a stable partition, so the result equals the
+// reference's: a stable sort by the transformed key.
+#include "common.cuh"
+
+namespace b200alg {
+
+constexpr int kRadix = 256;
+constexpr int kMaxPasses = 8;
+
+// Control words that live in TempHeader::reserved.
+enum : int {
+    kCtlTicket = 0,        // [0..7]  next tile id of each pass
+    kCtlSkip = 8,          // [8..15] 1 = every key has the same digit at this position
+    kCtlSrcIsAlt = 16,     // [16..23] 1 = this pass reads the alternate buffer
+    kCtlFinalInAlt = 24    // 1 = the sorted data ended in the alternate buffer
+};
+
+// Key transform: bits = raw ^ (sign(raw) ? xor_neg : xor_pos) covers every key type of
+// RadixSortOperations.tt:77-93 and the descending complement of :122-123.
+template <typename K> struct KeyXform {
+    K xor_neg, xor_pos;
+    __device__ __forceinline__ K operator()(K raw) const {
+        return raw ^ ((raw >> (sizeof(K) * 8 - 1)) ? xor_neg : xor_pos);
+    }
+};
+
+static bool key_xform_constants(int dtype, int order, uint64_t &xn, uint64_t &xp) {
+    const int bits = dtype_bytes(dtype) * 8;
+    const uint64_t all = bits == 64 ? ~0ull : ((1ull << bits) - 1);
+    const uint64_t sign = 1ull << (bits - 1);
+    const bool total = (order & B200ALG_SORT_FLOAT_TOTAL_ORDER) != 0;
+    switch (dtype) {
+    case B200ALG_U8: case B200ALG_U16: case B200ALG_U32: case B200ALG_U64: xn = 0; xp = 0; break;
+    case B200ALG_I8: case B200ALG_I16: case B200ALG_I32: case B200ALG_I64: xn = sign; xp = sign; break;
+    case B200ALG_F32: case B200ALG_F64:
+        // literal reference transform: u ^ (signMask | (~u >> (bits-1))), logical shift
+        if (total) { xn = all; xp = sign; } else { xn = sign; xp = sign | 1ull; }
+        break;
+    case B200ALG_F16:
+        // literal: u ^ (0x8000 | ((uint)~u >> 15)), the shifted term is 0x1FFFE | !sign
+        if (total) { xn = all; xp = sign; } else { xn = 0xFFFEull; xp = 0xFFFFull; }
+        break;
+    default: return false;
+    }
+    if (order & B200ALG_SORT_DESCENDING) { xn ^= all; xp ^= all; }
+    return true;
+}
+
+// ---- 1. histograms of all digit positions ----------------------------------------------
+constexpr int kHistoThreads = 512;
+constexpr int kHistoReplicas = 4;
+
+template <typename K>
+__global__ void __launch_bounds__(kHistoThreads)
+sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, KeyXform<K> xf, unsigned int *ghist) {
+    constexpr int P = sizeof(K);
+    __shared__ unsigned int sh[kHistoReplicas][P][kRadix];
+    for (int i = threadIdx.x; i < kHistoReplicas * P * kRadix; i += kHistoThreads) (&sh[0][0][0])[i] = 0u;
+    __syncthreads();
+    unsigned int(*mine)[kRadix] = sh[(threadIdx.x >> 5) % kHistoReplicas];
+    const int64_t step = (int64_t)gridDim.x * kHistoThreads;
+    const int64_t gtid = (int64_t)blockIdx.x * kHistoThreads + threadIdx.x;
+    auto count = [&](K raw) {
+        const K b = xf(raw);
+#pragma unroll
+        for (int p = 0; p < P; ++p) atomicAdd(&mine[p][(unsigned)(b >> (8 * p)) & 0xFFu], 1u);
+    };
+    if (stride == 1) {
+        constexpr int VEC = 16 / sizeof(K);
+        union V { uint4 u; K k[VEC]; };
+        int64_t head = (int64_t)(((16u - (unsigned)((uintptr_t)keys & 15u)) & 15u) / sizeof(K));
+        if (head > n) head = n;
+        const uint4 *vin = reinterpret_cast<const uint4 *>(keys + head);
+        const int64_t nvec = (n - head) / VEC;
+        const int64_t tail = head + nvec * VEC;
+        int64_t i = gtid;
+        for (; i + step < nvec; i += 2 * step) {
+            V a, b;
+            a.u = __ldg(vin + i);
+            b.u = __ldg(vin + i + step);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) count(a.k[k]);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) count(b.k[k]);
+        }
+        for (; i < nvec; i += step) {
+            V a;
+            a.u = __ldg(vin + i);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) count(a.k[k]);
+        }
+        if (blockIdx.x == 0) {
+            for (int64_t j = threadIdx.x; j < head; j += kHistoThreads) count(keys[j]);
+            for (int64_t j = tail + threadIdx.x; j < n; j += kHistoThreads) count(keys[j]);
+        }
+    } else {
+        for (int64_t i = gtid; i < n; i += step) count(keys[i * stride]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < P * kRadix; i += kHistoThreads) {
+        unsigned int c = 0;
+#pragma unroll
+        for (int r = 0; r < kHistoReplicas; ++r) c += (&sh[r][0][0])[i];
+        if (c) atomicAdd(ghist + i, c);
+    }
+}
+
+// ---- 2. global digit offsets, skipped passes, buffer schedule ---------------------------
+__global__ void __launch_bounds__(kRadix)
+sort_offsets_kernel(const unsigned int *ghist, unsigned int *gbase, TempHeader *hdr, int passes, unsigned int n) {
+    __shared__ unsigned int warp_sum[kRadix / 32];
+    __shared__ int s_skip;
+    const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
+    int src_is_alt = 0;
+    for (int p = 0; p < passes; ++p) {
+        if (d == 0) s_skip = 0;
+        __syncthreads();
+        const unsigned int c = ghist[p * kRadix + d];
+        if (c == n) s_skip = 1;
+        unsigned int incl = c;
+#pragma unroll
+        for (int k = 1; k < 32; k <<= 1) {
+            unsigned int up = __shfl_up_sync(0xffffffffu, incl, k);
+            if (lane >= k) incl += up;
+        }
+        if (lane == 31) warp_sum[warp] = incl;
+        __syncthreads();
+        unsigned int before = 0;
+        for (int w = 0; w < warp; ++w) before += warp_sum[w];
+        gbase[p * kRadix + d] = before + incl - c;
+        const int skip = s_skip;
+        if (d == 0) {
+            hdr->reserved[kCtlSkip + p] = (unsigned)skip;
+            hdr->reserved[kCtlSrcIsAlt + p] = (unsigned)src_is_alt;
+        }
+        if (!skip) src_is_alt ^= 1;
+        __syncthreads();
+    }
+    if (d == 0) hdr->reserved[kCtlFinalInAlt] = (unsigned)src_is_alt;
+}
+
+// ---- 3. one digit pass -------------------------------------------------------------------
+// Look-back words: the top two bits carry the state, the rest the count.
+template <typename SW> struct StatusWord;
+template <> struct StatusWord<unsigned int> {
+    static constexpr unsigned int kAgg = 1u << 30, kIncl = 2u << 30, kMask = (1u << 30) - 1u;
+    static __device__ __forceinline__ void st(unsigned int *p, unsigned int v) { st_relaxed_u32(p, v); }
+    static __device__ __forceinline__ unsigned int ld(const unsigned int *p) { return ld_relaxed_u32(p); }
+};
+template <> struct StatusWord<unsigned long long> {
+    static constexpr unsigned long long kAgg = 1ull << 62, kIncl = 2ull << 62, kMask = (1ull << 62) - 1ull;
+    static __device__ __forceinline__ void st(unsigned long long *p, unsigned long long v) { st_relaxed_u64(p, v); }
+    static __device__ __forceinline__ unsigned long long ld(const unsigned long long *p) { return ld_relaxed_u64(p); }
+};
+
+// What a pass partitions by.  RadixDigit: one 8-bit digit of the transformed key.
+// SplitterBucket: the number of splitters that are <= (key, global index) in the order
+// (transformed key, index) - used to split a shard into per-rank buckets before the
+// all-to-all of a multi-GPU sort; ties between equal keys are broken by position, which
+// keeps the partition balanced under heavy duplicates and stable.
+template <typename K> struct RadixDigit {
+    static constexpr bool kUsesIndex = false;
+    KeyXform<K> xf;
+    int shift;
+    __device__ __forceinline__ unsigned int operator()(K key, int64_t) const {
+        return (unsigned int)(xf(key) >> shift) & 0xFFu;
+    }
+};
+template <typename K> struct SplitterBucket {
+    static constexpr bool kUsesIndex = true;
+    KeyXform<K> xf;
+    const K *splitter_keys;
+    const int64_t *splitter_index;
+    int num_splitters;
+    int64_t index_base;
+    __device__ __forceinline__ unsigned int operator()(K key, int64_t local_index) const {
+        const K tk = xf(key);
+        const int64_t gi = index_base + local_index;
+        unsigned int b = 0;
+        for (int s = 0; s < num_splitters; ++s) {
+            const K sk = xf(splitter_keys[s]);
+            b += (sk < tk) || (sk == tk && splitter_index[s] <= gi);
+        }
+        return b;
+    }
+};
+
+struct NoValue {};
+template <typename V> struct ValueBytes { static constexpr int value = sizeof(V); };
+template <> struct ValueBytes<NoValue> { static constexpr int value = 0; };
+
+template <int BITS> __device__ __forceinline__ unsigned int match_digit(unsigned int digit) {
+#ifdef B200ALG_MATCH_BALLOT
+    unsigned int peers = 0xffffffffu;
+#pragma unroll
+    for (int b = 0; b < BITS; ++b) {
+        const bool bit = (digit >> b) & 1u;
+        const unsigned int m = __ballot_sync(0xffffffffu, bit);
+        peers &= bit ? m : ~m;
+    }
+    return peers;
+#else
+    return __match_any_sync(0xffffffffu, digit);
+#endif
+}
+
+template <typename K, typename V, bool KEEP_DIGITS, int THREADS, int ITEMS>
+struct OnesweepSmem {
+    static constexpr int TILE = THREADS * ITEMS;
+    static constexpr int VB = ValueBytes<V>::value;
+    static constexpr int STAGE = (int)sizeof(K) > VB ? (int)sizeof(K) : VB;
+    static constexpr size_t bytes = (size_t)TILE * STAGE + (size_t)(THREADS / 32) * kRadix * 4 + kRadix * 4 * 2 + 64 +
+                                    (KEEP_DIGITS ? (size_t)TILE : 0);
+};
+
+template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS>
+__global__ void __launch_bounds__(THREADS)
+onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, int pass, Digit dg,
+                TempHeader *hdr, const unsigned int *gbase_all, SW *status_all, int num_tiles) {
+    constexpr int WARPS = THREADS / 32;
+    constexpr int TILE = THREADS * ITEMS;
+    constexpr bool HAS_VALUES = ValueBytes<V>::value != 0;
+    using S = StatusWord<SW>;
+    static_assert(THREADS >= kRadix, "one thread per digit");
+
+    if (hdr->reserved[kCtlSkip + pass]) return;
+    const bool src_is_alt = hdr->reserved[kCtlSrcIsAlt + pass] != 0;
+    // Buffer 0 is the caller's (possibly strided) view, buffer 1 the dense alternate.
+    const K *src = src_is_alt ? buf1 : buf0;
+    K *dst = src_is_alt ? buf0 : buf1;
+    const int64_t src_stride = src_is_alt ? 1 : stride0;
+    const int64_t dst_stride = src_is_alt ? stride0 : 1;
+    const V *vsrc = src_is_alt ? val1 : val0;
+    V *vdst = src_is_alt ? val0 : val1;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
+    K *skeys = reinterpret_cast<K *>(smem_raw);
+    unsigned int *warp_hist = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE);  // [WARPS][256]
+    unsigned int *bin_excl = warp_hist + WARPS * kRadix;   // digit's first slot inside the tile
+    unsigned int *bin_goff = bin_excl + kRadix;            // global index of slot p is bin_goff[d] + p
+    unsigned int *misc = bin_goff + kRadix;                // [0] tile id, [1..8] warp sums
+    unsigned char *sdigit = reinterpret_cast<unsigned char *>(misc + 16);  // only when digits need the index
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    if (tid == 0) misc[0] = atomicAdd(&hdr->reserved[kCtlTicket + pass], 1u);
+    for (int i = tid; i < WARPS * kRadix; i += THREADS) warp_hist[i] = 0u;
+    __syncthreads();
+    const int tile = (int)misc[0];
+    const int64_t tile_base = (int64_t)tile * TILE;
+    const int valid = (int)((n - tile_base) < TILE ? (n - tile_base) : TILE);
+
+    // Keys in warp-striped order: item i of lane l is element warp*32*ITEMS + i*32 + l.
+    K key[ITEMS];
+    unsigned int digit[ITEMS];
+    const int warp_base = warp * 32 * ITEMS + lane;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int local = warp_base + i * 32;
+        if (local < valid) {
+            key[i] = src[(tile_base + local) * src_stride];
+            digit[i] = dg(key[i], tile_base + local);
+        } else {
+            key[i] = K(0);
+            digit[i] = 0xFFu;  // padding ranks behind every real key of the last tile
+        }
+    }
+
+    // Early counts: per-warp digit histograms, published before the ranking work.
+    unsigned int *my_hist = warp_hist + warp * kRadix;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) atomicAdd(my_hist + digit[i], 1u);
+    __syncthreads();
+
+    // Two look-back arrays alternate between the passes that run; this pass clears the
+    // slots the next one will use (the previous pass, their last user, has completed).
+    SW *status = status_all + (src_is_alt ? (size_t)num_tiles * kRadix : 0);
+    SW *status_next = status_all + (src_is_alt ? 0 : (size_t)num_tiles * kRadix);
+    unsigned int tile_count = 0;
+    if (tid < kRadix) {
+        status_next[(size_t)tile * kRadix + tid] = 0;
+        // warp_hist[w][d] becomes the number of d-keys in warps before w.
+        unsigned int run = 0;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const unsigned int c = warp_hist[w * kRadix + tid];
+            warp_hist[w * kRadix + tid] = run;
+            run += c;
+        }
+        tile_count = run;
+        S::st(status + (size_t)tile * kRadix + tid, (tile == 0 ? S::kIncl : S::kAgg) | (SW)tile_count);
+        // exclusive scan of the digit counts over the 256 digit threads
+        unsigned int incl = tile_count;
+#pragma unroll
+        for (int k = 1; k < 32; k <<= 1) {
+            unsigned int up = __shfl_up_sync(0xffffffffu, incl, k);
+            if (lane >= k) incl += up;
+        }
+        if (lane == 31) misc[1 + warp] = incl;
+        bin_excl[tid] = incl - tile_count;  // completed below
+    }
+    __syncthreads();
+    if (tid < kRadix) {
+        unsigned int before = 0;
+        for (int w = 0; w < warp; ++w) before += misc[1 + w];
+        bin_excl[tid] += before;
+    }
+    __syncthreads();
+
+    // Ranking: keys of one item that share a digit find each other with a warp match; the
+    // lowest such lane advances the warp's running count for that digit.
+    unsigned int pos[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const unsigned int d = digit[i];
+        const unsigned int peers = match_digit<8>(d);
+        const int leader = __ffs(peers) - 1;
+        unsigned int old = 0;
+        if (lane == leader) {
+            old = my_hist[d];
+            my_hist[d] = old + __popc(peers);
+        }
+        old = __shfl_sync(0xffffffffu, old, leader);
+        pos[i] = bin_excl[d] + old + __popc(peers & lanemask_lt());
+        __syncwarp();
+    }
+
+    // Decoupled look-back, one digit per thread.
+    if (tid < kRadix) {
+        unsigned int prefix = 0;
+        if (tile > 0) {
+            bool gave_up = false;
+            for (int t = tile - 1; t >= 0; --t) {
+                const SW *slot = status + (size_t)t * kRadix + tid;
+                SW w = S::ld(slot);
+                unsigned int spins = 0;
+                while ((w & ~S::kMask) == 0) {
+                    if (++spins > kMaxSpin) { gave_up = true; break; }
+                    __nanosleep(20);
+                    w = S::ld(slot);
+                }
+                if (gave_up) break;
+                prefix += (unsigned int)(w & S::kMask);
+                if (w & S::kIncl) break;
+            }
+            if (gave_up) atomicExch(&hdr->wait_limit_hit, 1u);
+            S::st(status + (size_t)tile * kRadix + tid, S::kIncl | (SW)(prefix + tile_count));
+        }
+        bin_goff[tid] = gbase_all[pass * kRadix + tid] + prefix - bin_excl[tid];
+    }
+
+    // Scatter through shared memory so that global writes run along digit segments.
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        skeys[pos[i]] = key[i];
+        if constexpr (Digit::kUsesIndex) sdigit[pos[i]] = (unsigned char)digit[i];
+    }
+    __syncthreads();
+
+    unsigned int out_idx[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int p = tid + i * THREADS;
+        if (p < valid) {
+            const K k = skeys[p];
+            unsigned int d;
+            if constexpr (Digit::kUsesIndex) d = sdigit[p]; else d = dg(k, 0);
+            out_idx[i] = bin_goff[d] + (unsigned int)p;
+            dst[(int64_t)out_idx[i] * dst_stride] = k;
+        }
+    }
+
+    if constexpr (HAS_VALUES) {
+        V *svals = reinterpret_cast<V *>(smem_raw);
+        V val[ITEMS];
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int local = warp_base + i * 32;
+            if (local < valid) val[i] = vsrc[tile_base + local];
+        }
+        __syncthreads();  // every key has left the staging buffer
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int local = warp_base + i * 32;
+            if (local < valid) svals[pos[i]] = val[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int p = tid + i * THREADS;
+            if (p < valid) vdst[out_idx[i]] = svals[p];
+        }
+    }
+}
+
+// ---- 4. bring the result home when it ended in the alternate buffer ---------------------
+template <typename K, typename V>
+__global__ void __launch_bounds__(256)
+sort_copy_back_kernel(K *buf0, int64_t stride0, const K *buf1, V *val0, const V *val1, int64_t n, const TempHeader *hdr) {
+    if (!hdr->reserved[kCtlFinalInAlt]) return;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+        buf0[i * stride0] = buf1[i];
+        if constexpr (ValueBytes<V>::value != 0) val0[i] = val1[i];
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+struct SortLayout {
+    int passes;
+    int tile;
+    int64_t tiles;
+    bool wide_status;
+    int64_t off_ghist, off_gbase, off_status, control_bytes, off_keys, off_values, total;
+};
+
+template <typename K> struct SortTuning {
+    static constexpr int THREADS = 512;
+    static constexpr int ITEMS = sizeof(K) == 8 ? 8 : 16;
+};
+
+static SortLayout sort_layout(int key_bytes, int value_bytes, int64_t n) {
+    SortLayout L;
+    L.passes = key_bytes;
+    L.tile = 512 * (key_bytes == 8 ? 8 : 16);
+    L.tiles = ceil_div(n < 1 ? 1 : n, L.tile);
+    L.wide_status = n >= (1ll << 30);
+    L.off_ghist = sizeof(TempHeader);
+    L.off_gbase = L.off_ghist + (int64_t)kMaxPasses * kRadix * 4;
+    L.off_status = L.off_gbase + (int64_t)kMaxPasses * kRadix * 4;
+    L.control_bytes = L.off_status + round_up(2 * L.tiles * kRadix * (L.wide_status ? 8 : 4), 256);
+    L.off_keys = L.control_bytes;
+    L.off_values = L.off_keys + round_up(n * key_bytes, 256);
+    L.total = L.off_values + round_up(n * value_bytes, 256);
+    return L;
+}
+
+template <typename KernelT>
+static int allow_dynamic_smem(KernelT kernel, size_t bytes) {
+    // One cudaFuncSetAttribute per kernel instantiation, device and host thread.
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    B200ALG_CUDA_TRY(cudaGetDevice(&dev));
+    if (configured_device != dev) {
+        B200ALG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        configured_device = dev;
+    }
+    return B200ALG_OK;
+}
+
+template <typename K, typename V, typename SW>
+static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_t n, const KeyXform<K> &xf, void *temp,
+                      const SortLayout &L) {
+    constexpr int THREADS = SortTuning<K>::THREADS, ITEMS = SortTuning<K>::ITEMS;
+    using Smem = OnesweepSmem<K, V, false, THREADS, ITEMS>;
+    auto kernel = onesweep_kernel<K, V, SW, RadixDigit<K>, THREADS, ITEMS>;
+    {
+        const int rc = allow_dynamic_smem(kernel, Smem::bytes);
+        if (rc != B200ALG_OK) return rc;
+    }
+    char *t = (char *)temp;
+    TempHeader *hdr = (TempHeader *)temp;
+    unsigned int *ghist = (unsigned int *)(t + L.off_ghist);
+    unsigned int *gbase = (unsigned int *)(t + L.off_gbase);
+    SW *status = (SW *)(t + L.off_status);
+    K *alt_keys = (K *)(t + L.off_keys);
+    V *alt_vals = (V *)(t + L.off_values);
+
+    B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)L.control_bytes, s));
+    {
+        const int64_t per_block = (int64_t)kHistoThreads * (16 / sizeof(K)) * 2;
+        int64_t want = ceil_div(n, per_block);
+        const int64_t cap = (int64_t)sm_count() * (2048 / kHistoThreads);
+        const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+        sort_histogram_kernel<K><<<blocks, kHistoThreads, 0, s>>>(keys, stride, n, xf, ghist);
+        B200ALG_LAUNCH_CHECK();
+    }
+    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, L.passes, (unsigned int)n);
+    B200ALG_LAUNCH_CHECK();
+    for (int p = 0; p < L.passes; ++p) {
+        RadixDigit<K> dg{xf, p * 8};
+        kernel<<<(int)L.tiles, THREADS, Smem::bytes, s>>>(keys, stride, alt_keys, values, alt_vals, n, p, dg, hdr, gbase,
+                                                          status, (int)L.tiles);
+        B200ALG_LAUNCH_CHECK();
+    }
+    {
+        int64_t want = ceil_div(n, 256 * 8);
+        const int64_t cap = (int64_t)sm_count() * 8;
+        const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+        sort_copy_back_kernel<K, V><<<blocks, 256, 0, s>>>(keys, stride, alt_keys, values, alt_vals, n, hdr);
+        B200ALG_LAUNCH_CHECK();
+    }
+    return B200ALG_OK;
+}
+
+template <typename K, typename V>
+static int run_sort(cudaStream_t s, void *keys, int64_t stride, void *values, int64_t n, uint64_t xn, uint64_t xp,
+                    void *temp, const SortLayout &L) {
+    KeyXform<K> xf{(K)xn, (K)xp};
+    if (L.wide_status) return run_passes<K, V, unsigned long long>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
+    return run_passes<K, V, unsigned int>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
+}
+
+template <typename V>
+static int dispatch_key(cudaStream_t s, int key_bytes, void *keys, int64_t stride, void *values, int64_t n, uint64_t xn,
+                        uint64_t xp, void *temp, const SortLayout &L) {
+    switch (key_bytes) {
+    case 1: return run_sort<uint8_t, V>(s, keys, stride, values, n, xn, xp, temp, L);
+    case 2: return run_sort<uint16_t, V>(s, keys, stride, values, n, xn, xp, temp, L);
+    case 4: return run_sort<uint32_t, V>(s, keys, stride, values, n, xn, xp, temp, L);
+    case 8: return run_sort<uint64_t, V>(s, keys, stride, values, n, xn, xp, temp, L);
+    }
+    return B200ALG_UNSUPPORTED;
+}
+
+// ---- 5. stable partition of a shard into per-rank buckets (multi-GPU sort) ---------------
+template <typename K>
+__global__ void __launch_bounds__(256)
+bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K> dg, unsigned int *ghist) {
+    __shared__ unsigned int sh[8][kRadix];
+    for (int i = threadIdx.x; i < 8 * kRadix; i += 256) (&sh[0][0])[i] = 0u;
+    __syncthreads();
+    unsigned int *mine = sh[threadIdx.x >> 5];
+    const int64_t step = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += step) atomicAdd(mine + dg(keys[i], i), 1u);
+    __syncthreads();
+    unsigned int c = 0;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) c += sh[r][threadIdx.x];
+    if (c) atomicAdd(ghist + threadIdx.x, c);
+}
+
+__global__ void export_bucket_counts_kernel(const unsigned int *ghist, int64_t *counts, int num_buckets) {
+    if ((int)threadIdx.x < num_buckets) counts[threadIdx.x] = (int64_t)ghist[threadIdx.x];
+}
+
+template <typename K, typename V, typename SW>
+static int run_partition(cudaStream_t s, const K *keys, const V *values, int64_t n, const SplitterBucket<K> &dg,
+                         K *out_keys, V *out_values, int64_t *counts, int num_buckets, void *temp, const SortLayout &L) {
+    constexpr int THREADS = SortTuning<K>::THREADS, ITEMS = SortTuning<K>::ITEMS;
+    using Smem = OnesweepSmem<K, V, true, THREADS, ITEMS>;
+    auto kernel = onesweep_kernel<K, V, SW, SplitterBucket<K>, THREADS, ITEMS>;
+    {
+        const int rc = allow_dynamic_smem(kernel, Smem::bytes);
+        if (rc != B200ALG_OK) return rc;
+    }
+    char *t = (char *)temp;
+    TempHeader *hdr = (TempHeader *)temp;
+    unsigned int *ghist = (unsigned int *)(t + L.off_ghist);
+    unsigned int *gbase = (unsigned int *)(t + L.off_gbase);
+    SW *status = (SW *)(t + L.off_status);
+    B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)L.control_bytes, s));
+    {
+        int64_t want = ceil_div(n, 256 * 8);
+        const int64_t cap = (int64_t)sm_count() * 8;
+        const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+        bucket_histogram_kernel<K><<<blocks, 256, 0, s>>>(keys, n, dg, ghist);
+        B200ALG_LAUNCH_CHECK();
+    }
+    // One "pass": offsets of the buckets; the skip rule is off (n + 1 never matches a count),
+    // so the pass always moves the keys from buffer 0 (input) to buffer 1 (output).
+    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (unsigned int)n + 1u);
+    B200ALG_LAUNCH_CHECK();
+    export_bucket_counts_kernel<<<1, kRadix, 0, s>>>(ghist, counts, num_buckets);
+    B200ALG_LAUNCH_CHECK();
+    kernel<<<(int)L.tiles, THREADS, Smem::bytes, s>>>(const_cast<K *>(keys), 1, out_keys, const_cast<V *>(values), out_values,
+                                                      n, 0, dg, hdr, gbase, status, (int)L.tiles);
+    B200ALG_LAUNCH_CHECK();
+    return B200ALG_OK;
+}
+
+template <typename K, typename V>
+static int partition_typed(cudaStream_t s, const void *keys, const void *values, int64_t n, uint64_t xn, uint64_t xp,
+                           const void *splitter_keys, const int64_t *splitter_index, int num_splitters,
+                           int64_t index_base, void *out_keys, void *out_values, int64_t *counts, void *temp,
+                           const SortLayout &L) {
+    SplitterBucket<K> dg{KeyXform<K>{(K)xn, (K)xp}, (const K *)splitter_keys, splitter_index, num_splitters, index_base};
+    if (L.wide_status)
+        return run_partition<K, V, unsigned long long>(s, (const K *)keys, (const V *)values, n, dg, (K *)out_keys,
+                                                       (V *)out_values, counts, num_splitters + 1, temp, L);
+    return run_partition<K, V, unsigned int>(s, (const K *)keys, (const V *)values, n, dg, (K *)out_keys, (V *)out_values,
+                                             counts, num_splitters + 1, temp, L);
+}
+
+template <typename V>
+static int partition_key(cudaStream_t s, int kb, const void *keys, const void *values, int64_t n, uint64_t xn, uint64_t xp,
+                         const void *sk, const int64_t *si, int ns, int64_t base, void *ok, void *ov, int64_t *counts,
+                         void *temp, const SortLayout &L) {
+    switch (kb) {
+    case 1: return partition_typed<uint8_t, V>(s, keys, values, n, xn, xp, sk, si, ns, base, ok, ov, counts, temp, L);
+    case 2: return partition_typed<uint16_t, V>(s, keys, values, n, xn, xp, sk, si, ns, base, ok, ov, counts, temp, L);
+    case 4: return partition_typed<uint32_t, V>(s, keys, values, n, xn, xp, sk, si, ns, base, ok, ov, counts, temp, L);
+    case 8: return partition_typed<uint64_t, V>(s, keys, values, n, xn, xp, sk, si, ns, base, ok, ov, counts, temp, L);
+    }
+    return B200ALG_UNSUPPORTED;
+}
+
+static int sort_common(void *stream, void *keys, int64_t stride, void *values, int64_t n, int key_dtype, int value_bytes,
+                       int order, void *temp, int64_t temp_bytes) {
+    // Argument checks mirror VerifyArguments (RadixSortExtensions.cs:1340-1367).
+    if (!keys || !temp || (value_bytes && !values)) return B200ALG_INVALID_ARGUMENT;
+    if (n < 0 || stride < 1) return B200ALG_INVALID_ARGUMENT;
+    const int kb = dtype_bytes(key_dtype);
+    if (kb == 0) return B200ALG_UNSUPPORTED;
+    if (value_bytes != 0 && value_bytes != 1 && value_bytes != 2 && value_bytes != 4 && value_bytes != 8 && value_bytes != 16)
+        return B200ALG_UNSUPPORTED;
+    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (((uintptr_t)keys % kb) || (value_bytes && ((uintptr_t)values % value_bytes)) || ((uintptr_t)temp % 256))
+        return B200ALG_MISALIGNED;
+    uint64_t xn, xp;
+    if (!key_xform_constants(key_dtype, order, xn, xp)) return B200ALG_UNSUPPORTED;
+    const SortLayout L = sort_layout(kb, value_bytes, n);
+    if (temp_bytes < L.total) return B200ALG_TEMP_TOO_SMALL;
+    if (n == 0) return B200ALG_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (value_bytes) {
+    case 0: return dispatch_key<NoValue>(s, kb, keys, stride, values, n, xn, xp, temp, L);
+    case 1: return dispatch_key<uint8_t>(s, kb, keys, stride, values, n, xn, xp, temp, L);
+    case 2: return dispatch_key<uint16_t>(s, kb, keys, stride, values, n, xn, xp, temp, L);
+    case 4: return dispatch_key<uint32_t>(s, kb, keys, stride, values, n, xn, xp, temp, L);
+    case 8: return dispatch_key<uint64_t>(s, kb, keys, stride, values, n, xn, xp, temp, L);
+    case 16: return dispatch_key<uint4>(s, kb, keys, stride, values, n, xn, xp, temp, L);
+    }
+    return B200ALG_UNSUPPORTED;
+}
+
+}  // namespace b200alg
+
+using namespace b200alg;
+
+extern "C" int b200alg_radix_sort_temp_bytes(int key_dtype, int64_t n, int value_bytes, int64_t *out_bytes) {
+    if (!out_bytes || n < 0 || value_bytes < 0) return B200ALG_INVALID_ARGUMENT;
+    const int kb = dtype_bytes(key_dtype);
+    if (kb == 0) return B200ALG_UNSUPPORTED;
+    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    *out_bytes = sort_layout(kb, value_bytes, n).total;
+    return B200ALG_OK;
+}
+
+extern "C" int b200alg_radix_sort_keys(void *stream, void *keys, int64_t n, int64_t stride, int key_dtype, int order,
+                                       void *temp, int64_t temp_bytes) {
+    return sort_common(stream, keys, stride, nullptr, n, key_dtype, 0, order, temp, temp_bytes);
+}
+
+extern "C" int b200alg_radix_sort_pairs(void *stream, void *keys, void *values, int64_t n, int key_dtype, int value_bytes,
+                                        int order, void *temp, int64_t temp_bytes) {
+    if (value_bytes == 0) return B200ALG_INVALID_ARGUMENT;
+    return sort_common(stream, keys, 1, values, n, key_dtype, value_bytes, order, temp, temp_bytes);
+}
+
+extern "C" int b200alg_bucket_partition_temp_bytes(int key_dtype, int64_t n, int64_t *out_bytes) {
+    if (!out_bytes || n < 0) return B200ALG_INVALID_ARGUMENT;
+    const int kb = dtype_bytes(key_dtype);
+    if (kb == 0) return B200ALG_UNSUPPORTED;
+    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    *out_bytes = sort_layout(kb, 0, n).control_bytes;
+    return B200ALG_OK;
+}
+
+extern "C" int b200alg_bucket_partition(void *stream, const void *keys, const void *values, int64_t n, int key_dtype,
+                                        int value_bytes, int order, const void *splitter_keys,
+                                        const int64_t *splitter_index, int num_splitters, int64_t index_base,
+                                        void *out_keys, void *out_values, int64_t *bucket_counts, void *temp,
+                                        int64_t temp_bytes) {
+    if (!keys || !out_keys || !bucket_counts || !temp) return B200ALG_INVALID_ARGUMENT;
+    if (value_bytes && (!values || !out_values)) return B200ALG_INVALID_ARGUMENT;
+    if (n < 0 || num_splitters < 0 || num_splitters > 254) return B200ALG_INVALID_ARGUMENT;
+    if (num_splitters && (!splitter_keys || !splitter_index)) return B200ALG_INVALID_ARGUMENT;
+    const int kb = dtype_bytes(key_dtype);
+    if (kb == 0) return B200ALG_UNSUPPORTED;
+    if (value_bytes != 0 && value_bytes != 4 && value_bytes != 8) return B200ALG_UNSUPPORTED;
+    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (((uintptr_t)keys % kb) || ((uintptr_t)out_keys % kb) || ((uintptr_t)temp % 256) || ((uintptr_t)bucket_counts % 8))
+        return B200ALG_MISALIGNED;
+    uint64_t xn, xp;
+    if (!key_xform_constants(key_dtype, order, xn, xp)) return B200ALG_UNSUPPORTED;
+    const SortLayout L = sort_layout(kb, 0, n);
+    if (temp_bytes < L.control_bytes) return B200ALG_TEMP_TOO_SMALL;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n == 0) {
+        B200ALG_CUDA_TRY(cudaMemsetAsync(bucket_counts, 0, sizeof(int64_t) * (num_splitters + 1), s));
+        return B200ALG_OK;
+    }
+    switch (value_bytes) {
+    case 0: return partition_key<NoValue>(s, kb, keys, values, n, xn, xp, splitter_keys, splitter_index, num_splitters,
+                                          index_base, out_keys, out_values, bucket_counts, temp, L);
+    case 4: return partition_key<uint32_t>(s, kb, keys, values, n, xn, xp, splitter_keys, splitter_index, num_splitters,
+                                           index_base, out_keys, out_values, bucket_counts, temp, L);
+    case 8: return partition_key<uint64_t>(s, kb, keys, values, n, xn, xp, splitter_keys, splitter_index, num_splitters,
+                                           index_base, out_keys, out_values, bucket_counts, temp, L);
+    }
+    return B200ALG_UNSUPPORTED;
+}

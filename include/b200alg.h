@@ -1,0 +1,152 @@
+/*
+ * b200alg - data-parallel primitives (radix sort, scan, reduce, histogram) for NVIDIA
+ * B200 (sm_100a) behind the ILGPU.Algorithms API.
+ *
+ * C ABI: plain pointers and sizes only.  Every pointer named `stream` is a CUstream /
+ * cudaStream_t (NULL = the legacy default stream); every data pointer is a device
+ * address in the CUDA context that is current on the calling thread.  All work is
+ * enqueued on `stream`; no function synchronises with the host unless its comment says
+ * so.  The library allocates no device memory: scratch space comes from the caller
+ * (`temp`, sized by the *_temp_bytes helpers).  No pointer is retained after return.
+ * Concurrent calls are legal only with distinct temp buffers.
+ *
+ * Each entry point cites the ILGPU item it replaces (file:line inside the ILGPU source
+ * tree, Src/ILGPU.Algorithms unless another directory is given).
+ */
+#ifndef B200ALG_H
+#define B200ALG_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200ALG_VERSION 100 /* major*10000 + minor*100 + patch */
+
+/* Element types.  Sort keys accept all of them (the 11 key types of
+ * RadixSortOperations.tt:26-125); scan / reduce / histogram accept the six "atomic
+ * numeric types" I32, U32, I64, U64, F32, F64 (ScanReduceOperations.tt:20-74,
+ * HistogramOperations.tt:30-41). */
+typedef enum {
+    B200ALG_I8 = 0, B200ALG_U8 = 1, B200ALG_I16 = 2, B200ALG_U16 = 3,
+    B200ALG_I32 = 4, B200ALG_U32 = 5, B200ALG_I64 = 6, B200ALG_U64 = 7,
+    B200ALG_F16 = 8, B200ALG_F32 = 9, B200ALG_F64 = 10
+} b200alg_dtype;
+
+/* Scan / reduce operations: Add*, Max*, Min* of ScanReduceOperations.tt:20-26. */
+typedef enum { B200ALG_ADD = 0, B200ALG_MAX = 1, B200ALG_MIN = 2 } b200alg_op;
+
+/* Sort order flags.  DESCENDING selects the Descending* structs
+ * (RadixSortOperations.tt:100-125).  FLOAT_TOTAL_ORDER is an opt-in that orders
+ * F16/F32/F64 keys numerically (IEEE total order); without it float keys follow the
+ * reference's ExtractRadixBits literally (RadixSortOperations.tt:81-89). */
+#define B200ALG_SORT_ASCENDING 0
+#define B200ALG_SORT_DESCENDING 1
+#define B200ALG_SORT_FLOAT_TOTAL_ORDER 2
+
+/* Named histogram bin locators (the reference leaves IComputeSingleBinOperation to user
+ * structs, IHistogramOperations.cs:19-78; a C ABI needs a closed set).
+ *  EQUAL_WIDTH_CLAMP: t = (x - lo) * (num_bins / (hi - lo)) with the scale computed once
+ *      in the input's floating type (double for integer inputs); bin = floor(t) clamped
+ *      to [0, num_bins-1]; NaN -> bin 0.
+ *  MODULO: the reference tests' ModuloBin*Operation (ILGPU.Algorithms.Tests/
+ *      HistogramTests.tt:83-94): |x % num_bins| for integers, (int)|fmod(x, num_bins)|
+ *      for floats. */
+typedef enum { B200ALG_LOCATOR_EQUAL_WIDTH_CLAMP = 0, B200ALG_LOCATOR_MODULO = 1 } b200alg_locator;
+
+typedef enum {
+    B200ALG_OK = 0,
+    B200ALG_INVALID_ARGUMENT = 1,   /* null pointer, negative size, bad stride */
+    B200ALG_UNSUPPORTED = 2,        /* dtype / op / value size outside the closed set */
+    B200ALG_TEMP_TOO_SMALL = 3,
+    B200ALG_CUDA_ERROR = 4,         /* see b200alg_last_cuda_error() */
+    B200ALG_WAIT_LIMIT = 5,         /* a device-side wait ran out (reported by b200alg_device_status) */
+    B200ALG_MISALIGNED = 6,         /* a pointer is not aligned to its element size / temp not to 256 */
+    B200ALG_TOO_LARGE = 7           /* n beyond INT32_MAX (ErrorMessages.NotSupportedArrayView64) */
+} b200alg_status;
+
+int b200alg_version(void);
+const char *b200alg_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
+int b200alg_last_cuda_error(void);
+
+/* ---- radix sort -------------------------------------------------------------------
+ * Replaces the lambdas returned by CreateRadixSort (RadixSortExtensions.cs:1130-1337)
+ * and CreateRadixSortPairs (:1017-1118).  In place, LSD, stable.  `order` is a bit-or of
+ * the B200ALG_SORT_* flags. */
+
+/* Native counterpart of ComputeRadixSortTempStorageSize (:419-447) and
+ * ComputeRadixSortPairsTempStorageSize (:384-404); result in bytes (a multiple of 256).
+ * value_bytes = 0 for keys only. */
+int b200alg_radix_sort_temp_bytes(int key_dtype, int64_t n, int value_bytes, int64_t *out_bytes);
+
+/* keys: n elements `stride` elements apart (ArrayView1D<T, TStride>; dense = 1). */
+int b200alg_radix_sort_keys(void *stream, void *keys, int64_t n, int64_t stride, int key_dtype,
+                            int order, void *temp, int64_t temp_bytes);
+
+/* values: n dense elements of value_bytes (1, 2, 4, 8 or 16) each, permuted like the keys. */
+int b200alg_radix_sort_pairs(void *stream, void *keys, void *values, int64_t n, int key_dtype,
+                             int value_bytes, int order, void *temp, int64_t temp_bytes);
+
+/* Stable partition of a shard into num_splitters + 1 buckets: the first step of a sort
+ * that spans several GPUs (new surface; the reference has no multi-device sort, its only
+ * multi-GPU facility is peer access, Src/ILGPU/Runtime/PeerAccess.cs).  Element i goes to
+ * bucket #{s : (splitter_keys[s], splitter_index[s]) <= (keys[i], index_base + i)} in the
+ * order (transformed key, index); inside a bucket the input order is kept.  out_keys /
+ * out_values receive the buckets one after the other, bucket_counts (int64, device) their
+ * sizes.  Splitters are device arrays and must be ascending in that order.
+ * value_bytes in {0, 4, 8}. */
+int b200alg_bucket_partition_temp_bytes(int key_dtype, int64_t n, int64_t *out_bytes);
+int b200alg_bucket_partition(void *stream, const void *keys, const void *values, int64_t n, int key_dtype,
+                             int value_bytes, int order, const void *splitter_keys,
+                             const int64_t *splitter_index, int num_splitters, int64_t index_base,
+                             void *out_keys, void *out_values, int64_t *bucket_counts, void *temp,
+                             int64_t temp_bytes);
+
+/* ---- scan -------------------------------------------------------------------------
+ * Replaces the lambda of CreateScan (ScanExtensions.cs:930-959 -> SinglePassScanKernel
+ * :530-706).  out[i*out_stride] = fold(op, in[0..i]) (inclusive) or fold(op, in[0..i-1])
+ * with out[0] = Identity (exclusive).  in == out is allowed when the strides match. */
+int b200alg_scan_temp_bytes(int dtype, int64_t n, int64_t *out_bytes); /* ComputeScanTempStorageSize :158-170 */
+int b200alg_scan(void *stream, const void *in, int64_t in_stride, void *out, int64_t out_stride,
+                 int64_t n, int dtype, int op, int inclusive, void *temp, int64_t temp_bytes);
+/* Same, with the running value that precedes in[0] read from device memory
+ * (`carry_in`, one element, may be NULL = Identity): what a sharded scan uses to add
+ * the total of the lower ranks.  New surface; the reference has no multi-device scan. */
+int b200alg_scan_carry(void *stream, const void *in, int64_t in_stride, void *out, int64_t out_stride,
+                       int64_t n, int dtype, int op, int inclusive, const void *carry_in,
+                       void *temp, int64_t temp_bytes);
+
+/* ---- reduce -----------------------------------------------------------------------
+ * Replaces the lambda of CreateReduction (ReductionExtensions.cs:135-167): out[0] is set
+ * to Identity and then folded with every input element.  n >= 1. */
+int b200alg_reduce(void *stream, const void *in, int64_t stride, int64_t n, int dtype, int op, void *out);
+
+/* ---- histogram --------------------------------------------------------------------
+ * Replaces the lambdas of CreateHistogram / CreateHistogramUnchecked
+ * (HistogramExtensions.cs:293-354, :371-427) with the single-bin adapter
+ * (HistogramLaunchers.tt:52-101).  bins[locator(x)] += 1 for every element; bins are
+ * accumulated into, never cleared.  overflow (int32[1], may be NULL = unchecked variant)
+ * gets |= 1 when an increment started from the bin type's MaxValue
+ * (HistogramOperations.tt:36-40). */
+int b200alg_histogram(void *stream, const void *in, int64_t stride, int64_t n, int in_dtype,
+                      int locator, double lo, double hi, void *bins, int64_t num_bins, int bin_dtype,
+                      void *overflow);
+
+/* ---- helpers on the path's edges --------------------------------------------------- */
+/* InitializeExtensions.cs (CreateInitializer): view[i*stride] = *value (elem_bytes bytes, host pointer). */
+int b200alg_initialize(void *stream, void *view, int64_t stride, int64_t n, int elem_bytes, const void *value);
+/* SequenceExtensions.cs with the Int32/Int64/UInt32/UInt64 sequencers of Sequencers.tt:
+ * view[i] = (T)(start + i * step); dtype in {I32, U32, I64, U64}. */
+int b200alg_sequence(void *stream, void *view, int64_t n, int dtype, int64_t start, int64_t step);
+
+/* Device-side waits (decoupled look-back) are bounded; when one runs out the kernel
+ * records it in `temp` and finishes.  This call copies that record back and
+ * SYNCHRONISES `stream`: returns B200ALG_OK or B200ALG_WAIT_LIMIT. */
+int b200alg_device_status(void *stream, const void *temp);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ALG_H */

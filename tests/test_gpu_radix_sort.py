@@ -1,0 +1,172 @@
+"""GPU parity of the radix sort (keys and pairs) against the CPU oracle, through the C ABI.
+
+Mirrors ILGPU.Algorithms.Tests/RadixSortExtensionTests.tt:144-432 (worst case = inverted
+ramp, best case = sorted ramp, constants, ascending and descending, provider API, pairs)
+and adds what those tests leave unpinned: random keys of every key type, duplicate keys
+with payload = index (stability), negative and special float keys, strided views.
+Everything is bit-exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+from ilgpu_b200 import RadixSortOperations as Ops
+from oracle import cpu_oracle as oracle
+from tests.helpers import ATOMIC, EDGE_SIZES, NP, REFERENCE_SIZES, compute_inverted_sequence, compute_sequence, to_device, to_host
+
+pytestmark = pytest.mark.gpu
+
+ALL_KEYS = list(NP.keys())
+
+
+def _sort_keys(accelerator, op, host, stride=1):
+    dev = to_device(host)
+    view = dev[::stride] if stride != 1 else dev
+    temp = accelerator.Allocate1D(accelerator.ComputeRadixSortTempStorageSize(op, view.numel()), torch.int32)
+    accelerator.CreateRadixSort(op)(None, view, temp)
+    accelerator.CheckDeviceStatus(None, temp)
+    return to_host(dev)
+
+
+def _bits(a):
+    return a.view({1: np.uint8, 2: np.uint16, 4: np.uint32, 8: np.uint64}[a.dtype.itemsize])
+
+
+@pytest.mark.parametrize("tname", ATOMIC)
+@pytest.mark.parametrize("direction", ["Ascending", "Descending"])
+def test_reference_cases(accelerator, tname, direction):
+    op = getattr(Ops, direction + tname)
+    t = NP[tname]
+    for size in REFERENCE_SIZES:
+        ramp = compute_sequence(t, 0, 1, size)
+        inverted = compute_inverted_sequence(t, 0, 1, size)
+        expected = ramp if direction == "Ascending" else inverted
+        for seq in (inverted, ramp):  # worst case, best case
+            got = _sort_keys(accelerator, op, seq)
+            np.testing.assert_array_equal(got, expected)
+            np.testing.assert_array_equal(got, oracle.radix_sort(seq, descending=op.descending)[0])
+        consts = [0, 1] + ([] if tname.startswith("U") else [-1])
+        for c in consts:
+            seq = compute_sequence(t, c, 0, size)
+            np.testing.assert_array_equal(_sort_keys(accelerator, op, seq), seq)
+
+
+@pytest.mark.parametrize("tname", ATOMIC)
+def test_pairs_reference_case(accelerator, tname):
+    # RadixSortExtensionTests.tt:319-365: keys = values = inverted ramp
+    op = getattr(Ops, "Ascending" + tname)
+    for size in [127, 1027]:
+        seq = compute_inverted_sequence(NP[tname], 0, 1, size)
+        keys, values = to_device(seq), to_device(seq)
+        provider = accelerator.CreateRadixSortProvider(op, size, values.dtype)
+        provider.CreateRadixSortPairs(op)(None, keys, values)
+        accelerator.Synchronize()
+        ramp = compute_sequence(NP[tname], 0, 1, size)
+        np.testing.assert_array_equal(to_host(keys), ramp)
+        np.testing.assert_array_equal(to_host(values), ramp)
+        provider.Dispose()
+
+
+def _random_keys(tname, n, seed):
+    rng = np.random.default_rng(seed)
+    t = NP[tname]
+    bits = rng.integers(0, 2 ** (8 * np.dtype(t).itemsize), size=n, dtype=np.uint64, endpoint=False) \
+        if np.dtype(t).itemsize < 8 else rng.integers(0, 2 ** 64, size=n, dtype=np.uint64, endpoint=False)
+    raw = bits.astype({1: np.uint8, 2: np.uint16, 4: np.uint32, 8: np.uint64}[np.dtype(t).itemsize])
+    return raw.view(t)
+
+
+@pytest.mark.parametrize("tname", ALL_KEYS)
+@pytest.mark.parametrize("direction", ["Ascending", "Descending"])
+def test_random_keys_every_type(accelerator, tname, direction):
+    # Random bit patterns: for float types this includes negatives, NaNs, infinities and
+    # denormals; comparison is on the bit patterns.
+    op = getattr(Ops, direction + tname)
+    for n in [1027, 8193, 300_007]:
+        keys = _random_keys(tname, n, n)
+        expected = oracle.radix_sort(keys, descending=op.descending)[0]
+        got = _sort_keys(accelerator, op, keys)
+        np.testing.assert_array_equal(_bits(got), _bits(expected))
+
+
+@pytest.mark.parametrize("n", EDGE_SIZES + [(1 << 22) + 11])
+def test_uint32_sizes(accelerator, n):
+    keys = _random_keys("UInt32", n, n)
+    got = _sort_keys(accelerator, Ops.AscendingUInt32, keys)
+    np.testing.assert_array_equal(got, np.sort(keys, kind="stable"))
+
+
+@pytest.mark.parametrize("key_t,val_t", [("UInt64", "UInt32"), ("UInt32", "UInt32"), ("Int32", "Int64"),
+                                          ("Float", "UInt32"), ("UInt8", "UInt16"), ("Int16", "UInt8"),
+                                          ("Double", "Double")])
+@pytest.mark.parametrize("direction", ["Ascending", "Descending"])
+def test_pairs_stable_with_duplicates(accelerator, key_t, val_t, direction):
+    op = getattr(Ops, direction + key_t)
+    for n in [4097, 250_003]:
+        rng = np.random.default_rng(n)
+        keys = rng.integers(0, 50, size=n).astype(NP[key_t])   # heavy duplicates
+        if key_t in ("Int32", "Int16", "Float", "Double"):
+            keys = (keys - 25).astype(NP[key_t])
+        values = np.arange(n).astype(NP[val_t])                 # payload = original index (mod range)
+        ek, ev = oracle.radix_sort(keys, values, descending=op.descending)
+        dk, dv = to_device(keys), to_device(values)
+        temp = accelerator.Allocate1D(accelerator.ComputeRadixSortPairsTempStorageSize(op, dv.dtype, n), torch.int32)
+        accelerator.CreateRadixSortPairs(op)(None, dk, dv, temp)
+        accelerator.CheckDeviceStatus(None, temp)
+        np.testing.assert_array_equal(_bits(to_host(dk)), _bits(ek))
+        np.testing.assert_array_equal(to_host(dv), ev)
+
+
+def test_pairs_16_byte_values(accelerator):
+    n = 70_001
+    rng = np.random.default_rng(3)
+    keys = rng.integers(0, 1000, size=n).astype(np.uint32)
+    values = rng.integers(0, 2 ** 63, size=(n, 2)).astype(np.int64)
+    order = np.argsort(keys, kind="stable")
+    dk = to_device(keys)
+    dv = to_device(values.reshape(-1)).view(torch.complex128)  # any 16-byte element type
+    op = Ops.AscendingUInt32
+    temp = accelerator.Allocate1D(accelerator.ComputeRadixSortPairsTempStorageSize(op, dv.dtype, n), torch.int32)
+    accelerator.CreateRadixSortPairs(op)(None, dk, dv, temp)
+    np.testing.assert_array_equal(to_host(dk), keys[order])
+    np.testing.assert_array_equal(to_host(dv.view(torch.float64).view(torch.int64)).reshape(n, 2), values[order])
+
+
+def test_zipf_pairs_skips_constant_digits(accelerator):
+    # 64-bit keys whose upper four bytes are all zero: half of the digit passes are skipped.
+    from ilgpu_b200 import synthetic
+    n = 1 << 20
+    keys = synthetic.zipf_uint64(n, seed=4)
+    values = np.arange(n, dtype=np.uint32)
+    ek, ev = oracle.radix_sort(keys, values)
+    dk, dv = to_device(keys), to_device(values)
+    op = Ops.AscendingUInt64
+    temp = accelerator.Allocate1D(accelerator.ComputeRadixSortPairsTempStorageSize(op, dv.dtype, n), torch.int32)
+    accelerator.CreateRadixSortPairs(op)(None, dk, dv, temp)
+    np.testing.assert_array_equal(to_host(dk), ek)
+    np.testing.assert_array_equal(to_host(dv), ev)
+
+
+def test_float_total_order_opt_in(accelerator):
+    x = np.asarray([3.5, -1.0, 0.0, -0.0, -7.25, 2.0, np.inf, -np.inf, 1e-40, -1e-40] * 300, dtype=np.float32)
+    dev = to_device(x)
+    op = Ops.AscendingFloat
+    temp = accelerator.Allocate1D(accelerator.ComputeRadixSortTempStorageSize(op, x.size), torch.int32)
+    accelerator.CreateRadixSort(op, float_total_order=True)(None, dev, temp)
+    np.testing.assert_array_equal(to_host(dev), np.sort(x, kind="stable"))
+
+
+def test_strided_keys(accelerator):
+    n, stride = 20_011, 3
+    storage = _random_keys("UInt32", n * stride, 99)
+    got = _sort_keys(accelerator, Ops.AscendingUInt32, storage, stride=stride)
+    expected = storage.copy()
+    expected[::stride] = np.sort(storage[::stride])
+    np.testing.assert_array_equal(got, expected)   # elements between the strides untouched
+
+
+def test_literal_two_bit_restatement_agrees(accelerator):
+    # the 2-bit, two-kernel CPU path itself (not only its closed form) on a small case
+    keys = _random_keys("Int32", 1027, 5)
+    literal = oracle.radix_sort(keys, literal=True)[0]
+    np.testing.assert_array_equal(_sort_keys(accelerator, Ops.AscendingInt32, keys), literal)
