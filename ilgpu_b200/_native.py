@@ -10,7 +10,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200alg.so")
+# B200ALG_LIBRARY overrides the path of the shared library (e.g. a differently tuned build).
+LIB_PATH = os.environ.get("B200ALG_LIBRARY") or os.path.join(_HERE, "libb200alg.so")
 
 # status codes (include/b200alg.h)
 OK, INVALID_ARGUMENT, UNSUPPORTED, TEMP_TOO_SMALL, CUDA_ERROR, WAIT_LIMIT, MISALIGNED, TOO_LARGE = range(8)

@@ -15,6 +15,8 @@
 // reference's: a stable sort by the transformed key.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace b200alg {
 
 constexpr int kRadix = 256;
@@ -35,6 +37,10 @@ template <typename K> struct KeyXform {
     __device__ __forceinline__ K operator()(K raw) const {
         return raw ^ ((raw >> (sizeof(K) * 8 - 1)) ? xor_neg : xor_pos);
     }
+};
+// Ascending unsigned keys need no transform at all.
+template <typename K> struct KeyIdentity {
+    __device__ __forceinline__ K operator()(K raw) const { return raw; }
 };
 
 static bool key_xform_constants(int dtype, int order, uint64_t &xn, uint64_t &xp) {
@@ -171,9 +177,9 @@ template <> struct StatusWord<unsigned long long> {
 // (transformed key, index) - used to split a shard into per-rank buckets before the
 // all-to-all of a multi-GPU sort; ties between equal keys are broken by position, which
 // keeps the partition balanced under heavy duplicates and stable.
-template <typename K> struct RadixDigit {
+template <typename K, typename XF = KeyXform<K>> struct RadixDigit {
     static constexpr bool kUsesIndex = false;
-    KeyXform<K> xf;
+    XF xf;
     int shift;
     __device__ __forceinline__ unsigned int operator()(K key, int64_t) const {
         return (unsigned int)(xf(key) >> shift) & 0xFFu;
@@ -202,19 +208,18 @@ struct NoValue {};
 template <typename V> struct ValueBytes { static constexpr int value = sizeof(V); };
 template <> struct ValueBytes<NoValue> { static constexpr int value = 0; };
 
-template <int BITS> __device__ __forceinline__ unsigned int match_digit(unsigned int digit) {
-#ifdef B200ALG_MATCH_BALLOT
+// Lanes of a warp that hold the same 8-bit digit: one ballot per digit bit (the hardware
+// match instruction serialises over the distinct values, ~30 of them for random digits).
+__device__ __forceinline__ unsigned int match_digit(unsigned int digit) {
     unsigned int peers = 0xffffffffu;
 #pragma unroll
-    for (int b = 0; b < BITS; ++b) {
-        const bool bit = (digit >> b) & 1u;
-        const unsigned int m = __ballot_sync(0xffffffffu, bit);
-        peers &= bit ? m : ~m;
+    for (int b = 0; b < 8; ++b) {
+        int ext;  // bit b replicated over the word
+        asm("bfe.s32 %0, %1, %2, 1;" : "=r"(ext) : "r"(digit), "r"(b));
+        const unsigned int m = __ballot_sync(0xffffffffu, ext != 0);
+        peers &= ~(m ^ (unsigned int)ext);
     }
     return peers;
-#else
-    return __match_any_sync(0xffffffffu, digit);
-#endif
 }
 
 template <typename K, typename V, bool KEEP_DIGITS, int THREADS, int ITEMS>
@@ -226,79 +231,79 @@ struct OnesweepSmem {
                                     (KEEP_DIGITS ? (size_t)TILE : 0);
 };
 
-template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS>
-__global__ void __launch_bounds__(THREADS)
-onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, int pass, Digit dg,
-                TempHeader *hdr, const unsigned int *gbase_all, SW *status_all, int num_tiles) {
+// One tile of one digit pass.  FAST = the tile is full and both buffers are dense, so no
+// bounds checks and no stride arithmetic.
+template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS, bool FAST>
+__device__ __forceinline__ void onesweep_tile(const K *src, int64_t src_stride, K *dst, int64_t dst_stride, const V *vsrc,
+                                              V *vdst, int64_t n, int tile, const Digit &dg, TempHeader *hdr,
+                                              const unsigned int *gbase, SW *status, SW *status_next,
+                                              unsigned char *smem_raw) {
     constexpr int WARPS = THREADS / 32;
     constexpr int TILE = THREADS * ITEMS;
     constexpr bool HAS_VALUES = ValueBytes<V>::value != 0;
     using S = StatusWord<SW>;
-    static_assert(THREADS >= kRadix, "one thread per digit");
-
-    if (hdr->reserved[kCtlSkip + pass]) return;
-    const bool src_is_alt = hdr->reserved[kCtlSrcIsAlt + pass] != 0;
-    // Buffer 0 is the caller's (possibly strided) view, buffer 1 the dense alternate.
-    const K *src = src_is_alt ? buf1 : buf0;
-    K *dst = src_is_alt ? buf0 : buf1;
-    const int64_t src_stride = src_is_alt ? 1 : stride0;
-    const int64_t dst_stride = src_is_alt ? stride0 : 1;
-    const V *vsrc = src_is_alt ? val1 : val0;
-    V *vdst = src_is_alt ? val0 : val1;
-
-    extern __shared__ __align__(16) unsigned char smem_raw[];
     using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
     K *skeys = reinterpret_cast<K *>(smem_raw);
-    unsigned int *warp_hist = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE);  // [WARPS][256]
-    unsigned int *bin_excl = warp_hist + WARPS * kRadix;   // digit's first slot inside the tile
+    unsigned int *warp_cnt = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE);  // [WARPS][256]
+    unsigned int *bin_excl = warp_cnt + WARPS * kRadix;    // digit's first slot inside the tile
     unsigned int *bin_goff = bin_excl + kRadix;            // global index of slot p is bin_goff[d] + p
     unsigned int *misc = bin_goff + kRadix;                // [0] tile id, [1..8] warp sums
     unsigned char *sdigit = reinterpret_cast<unsigned char *>(misc + 16);  // only when digits need the index
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-
-    if (tid == 0) misc[0] = atomicAdd(&hdr->reserved[kCtlTicket + pass], 1u);
-    for (int i = tid; i < WARPS * kRadix; i += THREADS) warp_hist[i] = 0u;
-    __syncthreads();
-    const int tile = (int)misc[0];
     const int64_t tile_base = (int64_t)tile * TILE;
-    const int valid = (int)((n - tile_base) < TILE ? (n - tile_base) : TILE);
+    const int valid = FAST ? TILE : (int)((n - tile_base) < TILE ? (n - tile_base) : TILE);
 
     // Keys in warp-striped order: item i of lane l is element warp*32*ITEMS + i*32 + l.
     K key[ITEMS];
-    unsigned int digit[ITEMS];
     const int warp_base = warp * 32 * ITEMS + lane;
+    if (FAST) {
+        const K *p = src + tile_base + warp_base;
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-        const int local = warp_base + i * 32;
-        if (local < valid) {
-            key[i] = src[(tile_base + local) * src_stride];
-            digit[i] = dg(key[i], tile_base + local);
-        } else {
-            key[i] = K(0);
-            digit[i] = 0xFFu;  // padding ranks behind every real key of the last tile
+        for (int i = 0; i < ITEMS; ++i) key[i] = p[i * 32];
+    } else {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int local = warp_base + i * 32;
+            key[i] = local < valid ? src[(tile_base + local) * src_stride] : K(0);
         }
     }
 
-    // Early counts: per-warp digit histograms, published before the ranking work.
-    unsigned int *my_hist = warp_hist + warp * kRadix;
+    // Ranking inside the warp: keys of one item that share a digit find each other by
+    // ballots; the highest such lane advances the warp's count of that digit.  After the
+    // loop warp_cnt[warp][d] is the warp's number of d-keys.
+    unsigned int *my_cnt = warp_cnt + warp * kRadix;
+    const unsigned int lt = lanemask_lt();
+    unsigned int packed[ITEMS];  // (rank among the warp's keys of that digit) << 8 | digit
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) atomicAdd(my_hist + digit[i], 1u);
+    for (int i = 0; i < ITEMS; ++i) {
+        unsigned int d;
+        if (FAST) {
+            d = dg(key[i], tile_base + warp_base + i * 32);
+        } else {
+            const int local = warp_base + i * 32;
+            d = local < valid ? dg(key[i], tile_base + local) : 0xFFu;  // padding ranks behind every real key
+        }
+        const unsigned int peers = match_digit(d);
+        const unsigned int before = peers & lt;
+        int leader;  // highest lane among the peers
+        asm("bfind.u32 %0, %1;" : "=r"(leader) : "r"(peers));
+        unsigned int old = 0;
+        if (lane == leader) old = atomicAdd(my_cnt + d, (unsigned int)__popc(peers));
+        old = __shfl_sync(0xffffffffu, old, leader);
+        packed[i] = ((old + __popc(before)) << 8) | d;
+    }
     __syncthreads();
 
-    // Two look-back arrays alternate between the passes that run; this pass clears the
-    // slots the next one will use (the previous pass, their last user, has completed).
-    SW *status = status_all + (src_is_alt ? (size_t)num_tiles * kRadix : 0);
-    SW *status_next = status_all + (src_is_alt ? 0 : (size_t)num_tiles * kRadix);
     unsigned int tile_count = 0;
     if (tid < kRadix) {
         status_next[(size_t)tile * kRadix + tid] = 0;
-        // warp_hist[w][d] becomes the number of d-keys in warps before w.
+        // warp_cnt[w][d] becomes the number of d-keys in the warps before w.
         unsigned int run = 0;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const unsigned int c = warp_hist[w * kRadix + tid];
-            warp_hist[w * kRadix + tid] = run;
+            const unsigned int c = warp_cnt[w * kRadix + tid];
+            warp_cnt[w * kRadix + tid] = run;
             run += c;
         }
         tile_count = run;
@@ -316,27 +321,24 @@ onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, 
     __syncthreads();
     if (tid < kRadix) {
         unsigned int before = 0;
-        for (int w = 0; w < warp; ++w) before += misc[1 + w];
-        bin_excl[tid] += before;
+#pragma unroll
+        for (int w = 0; w < kRadix / 32; ++w) before += (w < warp) ? misc[1 + w] : 0u;
+        const unsigned int excl = bin_excl[tid] + before;
+        bin_excl[tid] = excl;
+        // fold the digit's first slot into the per-warp offsets: one table lookup per key
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) warp_cnt[w * kRadix + tid] += excl;
     }
     __syncthreads();
 
-    // Ranking: keys of one item that share a digit find each other with a warp match; the
-    // lowest such lane advances the warp's running count for that digit.
+    // Scatter through shared memory so that global writes run along digit segments.
     unsigned int pos[ITEMS];
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
-        const unsigned int d = digit[i];
-        const unsigned int peers = match_digit<8>(d);
-        const int leader = __ffs(peers) - 1;
-        unsigned int old = 0;
-        if (lane == leader) {
-            old = my_hist[d];
-            my_hist[d] = old + __popc(peers);
-        }
-        old = __shfl_sync(0xffffffffu, old, leader);
-        pos[i] = bin_excl[d] + old + __popc(peers & lanemask_lt());
-        __syncwarp();
+        const unsigned int d = packed[i] & 0xFFu;
+        pos[i] = (packed[i] >> 8) + my_cnt[d];
+        skeys[pos[i]] = key[i];
+        if constexpr (Digit::kUsesIndex) sdigit[pos[i]] = (unsigned char)d;
     }
 
     // Decoupled look-back, one digit per thread.
@@ -360,14 +362,7 @@ onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, 
             if (gave_up) atomicExch(&hdr->wait_limit_hit, 1u);
             S::st(status + (size_t)tile * kRadix + tid, S::kIncl | (SW)(prefix + tile_count));
         }
-        bin_goff[tid] = gbase_all[pass * kRadix + tid] + prefix - bin_excl[tid];
-    }
-
-    // Scatter through shared memory so that global writes run along digit segments.
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-        skeys[pos[i]] = key[i];
-        if constexpr (Digit::kUsesIndex) sdigit[pos[i]] = (unsigned char)digit[i];
+        bin_goff[tid] = gbase[tid] + prefix - bin_excl[tid];
     }
     __syncthreads();
 
@@ -375,12 +370,12 @@ onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, 
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const int p = tid + i * THREADS;
-        if (p < valid) {
+        if (FAST || p < valid) {
             const K k = skeys[p];
             unsigned int d;
             if constexpr (Digit::kUsesIndex) d = sdigit[p]; else d = dg(k, 0);
             out_idx[i] = bin_goff[d] + (unsigned int)p;
-            dst[(int64_t)out_idx[i] * dst_stride] = k;
+            if (FAST) dst[out_idx[i]] = k; else dst[(int64_t)out_idx[i] * dst_stride] = k;
         }
     }
 
@@ -390,21 +385,65 @@ onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, 
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
             const int local = warp_base + i * 32;
-            if (local < valid) val[i] = vsrc[tile_base + local];
+            if (FAST || local < valid) val[i] = vsrc[tile_base + local];
         }
         __syncthreads();  // every key has left the staging buffer
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
             const int local = warp_base + i * 32;
-            if (local < valid) svals[pos[i]] = val[i];
+            if (FAST || local < valid) svals[pos[i]] = val[i];
         }
         __syncthreads();
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
             const int p = tid + i * THREADS;
-            if (p < valid) vdst[out_idx[i]] = svals[p];
+            if (FAST || p < valid) vdst[out_idx[i]] = svals[p];
         }
     }
+}
+
+template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS>
+__global__ void __launch_bounds__(THREADS)
+onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, int pass, Digit dg,
+                TempHeader *hdr, const unsigned int *gbase_all, SW *status_all, int num_tiles) {
+    constexpr int WARPS = THREADS / 32;
+    constexpr int TILE = THREADS * ITEMS;
+    static_assert(THREADS >= kRadix, "one thread per digit");
+    using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
+
+    if (hdr->reserved[kCtlSkip + pass]) return;
+    const bool src_is_alt = hdr->reserved[kCtlSrcIsAlt + pass] != 0;
+    // Buffer 0 is the caller's (possibly strided) view, buffer 1 the dense alternate.
+    const K *src = src_is_alt ? buf1 : buf0;
+    K *dst = src_is_alt ? buf0 : buf1;
+    const int64_t src_stride = src_is_alt ? 1 : stride0;
+    const int64_t dst_stride = src_is_alt ? stride0 : 1;
+    const V *vsrc = src_is_alt ? val1 : val0;
+    V *vdst = src_is_alt ? val0 : val1;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned int *warp_cnt = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE);
+    unsigned int *misc = warp_cnt + WARPS * kRadix + 2 * kRadix;
+
+    const int tid = threadIdx.x;
+    if (tid == 0) misc[0] = atomicAdd(&hdr->reserved[kCtlTicket + pass], 1u);
+    for (int i = tid; i < WARPS * kRadix; i += THREADS) warp_cnt[i] = 0u;
+    __syncthreads();
+    const int tile = (int)misc[0];
+
+    // Two look-back arrays alternate between the passes that run; this pass clears the
+    // slots the next one will use (the previous pass, their last user, has completed).
+    SW *status = status_all + (src_is_alt ? (size_t)num_tiles * kRadix : 0);
+    SW *status_next = status_all + (src_is_alt ? 0 : (size_t)num_tiles * kRadix);
+    const unsigned int *gbase = gbase_all + pass * kRadix;
+
+    const bool fast = stride0 == 1 && (int64_t)(tile + 1) * TILE <= n;
+    if (fast)
+        onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, true>(src, 1, dst, 1, vsrc, vdst, n, tile, dg, hdr, gbase, status,
+                                                            status_next, smem_raw);
+    else
+        onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, false>(src, src_stride, dst, dst_stride, vsrc, vdst, n, tile, dg, hdr,
+                                                             gbase, status, status_next, smem_raw);
 }
 
 // ---- 4. bring the result home when it ended in the alternate buffer ---------------------
@@ -428,15 +467,21 @@ struct SortLayout {
     int64_t off_ghist, off_gbase, off_status, control_bytes, off_keys, off_values, total;
 };
 
+#ifndef B200ALG_SORT_THREADS
+#define B200ALG_SORT_THREADS 512
+#endif
+#ifndef B200ALG_SORT_ITEMS
+#define B200ALG_SORT_ITEMS 16
+#endif
 template <typename K> struct SortTuning {
-    static constexpr int THREADS = 512;
-    static constexpr int ITEMS = sizeof(K) == 8 ? 8 : 16;
+    static constexpr int THREADS = B200ALG_SORT_THREADS;
+    static constexpr int ITEMS = sizeof(K) == 8 ? B200ALG_SORT_ITEMS / 2 : B200ALG_SORT_ITEMS;
 };
 
 static SortLayout sort_layout(int key_bytes, int value_bytes, int64_t n) {
     SortLayout L;
     L.passes = key_bytes;
-    L.tile = 512 * (key_bytes == 8 ? 8 : 16);
+    L.tile = B200ALG_SORT_THREADS * (key_bytes == 8 ? B200ALG_SORT_ITEMS / 2 : B200ALG_SORT_ITEMS);
     L.tiles = ceil_div(n < 1 ? 1 : n, L.tile);
     L.wide_status = n >= (1ll << 30);
     L.off_ghist = sizeof(TempHeader);
@@ -462,12 +507,12 @@ static int allow_dynamic_smem(KernelT kernel, size_t bytes) {
     return B200ALG_OK;
 }
 
-template <typename K, typename V, typename SW>
+template <typename K, typename V, typename SW, typename XF>
 static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_t n, const KeyXform<K> &xf, void *temp,
                       const SortLayout &L) {
     constexpr int THREADS = SortTuning<K>::THREADS, ITEMS = SortTuning<K>::ITEMS;
     using Smem = OnesweepSmem<K, V, false, THREADS, ITEMS>;
-    auto kernel = onesweep_kernel<K, V, SW, RadixDigit<K>, THREADS, ITEMS>;
+    auto kernel = onesweep_kernel<K, V, SW, RadixDigit<K, XF>, THREADS, ITEMS>;
     {
         const int rc = allow_dynamic_smem(kernel, Smem::bytes);
         if (rc != B200ALG_OK) return rc;
@@ -492,7 +537,9 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
     sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, L.passes, (unsigned int)n);
     B200ALG_LAUNCH_CHECK();
     for (int p = 0; p < L.passes; ++p) {
-        RadixDigit<K> dg{xf, p * 8};
+        RadixDigit<K, XF> dg;
+        if constexpr (std::is_same<XF, KeyXform<K>>::value) dg.xf = xf;
+        dg.shift = p * 8;
         kernel<<<(int)L.tiles, THREADS, Smem::bytes, s>>>(keys, stride, alt_keys, values, alt_vals, n, p, dg, hdr, gbase,
                                                           status, (int)L.tiles);
         B200ALG_LAUNCH_CHECK();
@@ -511,8 +558,13 @@ template <typename K, typename V>
 static int run_sort(cudaStream_t s, void *keys, int64_t stride, void *values, int64_t n, uint64_t xn, uint64_t xp,
                     void *temp, const SortLayout &L) {
     KeyXform<K> xf{(K)xn, (K)xp};
-    if (L.wide_status) return run_passes<K, V, unsigned long long>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
-    return run_passes<K, V, unsigned int>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
+    const bool identity = xn == 0 && xp == 0;
+    if (L.wide_status) {
+        if (identity) return run_passes<K, V, unsigned long long, KeyIdentity<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
+        return run_passes<K, V, unsigned long long, KeyXform<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
+    }
+    if (identity) return run_passes<K, V, unsigned int, KeyIdentity<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
+    return run_passes<K, V, unsigned int, KeyXform<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
 }
 
 template <typename V>
