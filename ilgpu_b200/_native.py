@@ -14,7 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("B200ALG_LIBRARY") or os.path.join(_HERE, "libb200alg.so")
 
 # status codes (include/b200alg.h)
-OK, INVALID_ARGUMENT, UNSUPPORTED, TEMP_TOO_SMALL, CUDA_ERROR, WAIT_LIMIT, MISALIGNED, TOO_LARGE = range(8)
+OK, INVALID_ARGUMENT, UNSUPPORTED, TEMP_TOO_SMALL, CUDA_ERROR, WAIT_LIMIT, MISALIGNED, TOO_LARGE, STATIC_LIMIT = range(9)
 
 # dtype codes
 I8, U8, I16, U16, I32, U32, I64, U64, F16, F32, F64 = range(11)
@@ -37,6 +37,7 @@ SIGNATURES = {
     "b200alg_scan_temp_bytes": (_int, [_int, _i64, ctypes.POINTER(_i64)]),
     "b200alg_scan": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _int, _int, _int, _vp, _i64]),
     "b200alg_scan_carry": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _int, _int, _int, _vp, _vp, _i64]),
+    "b200alg_scan_static": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _int, _int, _int]),
     "b200alg_reduce": (_int, [_vp, _vp, _i64, _i64, _int, _int, _vp]),
     "b200alg_histogram": (_int, [_vp, _vp, _i64, _i64, _int, _int, _dbl, _dbl, _vp, _i64, _int, _vp]),
     "b200alg_initialize": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),

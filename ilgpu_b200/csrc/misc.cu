@@ -53,6 +53,7 @@ extern "C" const char *b200alg_status_string(int status) {
     case B200ALG_WAIT_LIMIT: return "a device-side wait exceeded its iteration limit";
     case B200ALG_MISALIGNED: return "pointer not aligned";
     case B200ALG_TOO_LARGE: return "more than INT32_MAX elements";
+    case B200ALG_STATIC_LIMIT: return "more elements than the built-in scratch of this entry point covers";
     }
     return "unknown status";
 }

@@ -297,3 +297,41 @@ extern "C" int b200alg_scan(void *stream, const void *in, int64_t in_stride, voi
                             int dtype, int op, int inclusive, void *temp, int64_t temp_bytes) {
     return b200alg_scan_carry(stream, in, in_stride, out, out_stride, n, dtype, op, inclusive, nullptr, temp, temp_bytes);
 }
+
+// ---- scan without caller-provided scratch ------------------------------------------------
+// Some callers can neither size nor allocate a temp view: code that runs where device
+// allocation is off the table (a host callback on a stream, a real-time loop that may not
+// take the allocator's lock, a plug-in that is handed input and output views and nothing
+// else).  For them the tile descriptors of the chained scan live in this fixed array,
+// which every GPU that loads the library carries until the process exits.
+constexpr int64_t kStaticScanMaxElements = 1ll << 26;
+constexpr size_t kStaticScanScratchBytes = sizeof(TempHeader) + (size_t)(kStaticScanMaxElements / 2048) * 24;
+static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScanScratchBytes];
+
+// Device address of the array on the current device.  The array's name is only a handle on
+// the host side, so the address is asked for once per device, with that device current.
+static int static_scan_scratch(void **out) {
+    static void *address[64] = {nullptr};
+    int dev = 0;
+    B200ALG_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return B200ALG_UNSUPPORTED;
+    if (address[dev] == nullptr) {
+        void *p = nullptr;
+        B200ALG_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scan_scratch));
+        address[dev] = p;
+    }
+    *out = address[dev];
+    return B200ALG_OK;
+}
+
+extern "C" int b200alg_scan_static(void *stream, const void *in, int64_t in_stride, void *out, int64_t out_stride,
+                                   int64_t n, int dtype, int op, int inclusive) {
+    if (n > kStaticScanMaxElements) return B200ALG_STATIC_LIMIT;
+    void *scratch = nullptr;
+    const int rc = static_scan_scratch(&scratch);
+    if (rc != B200ALG_OK) return rc;
+    // Same launch sequence as b200alg_scan: it clears the descriptors it is about to use, so
+    // whatever the previous call left in the array does not matter.
+    return b200alg_scan_carry(stream, in, in_stride, out, out_stride, n, dtype, op, inclusive, nullptr, scratch,
+                              (int64_t)kStaticScanScratchBytes);
+}

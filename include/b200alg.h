@@ -63,7 +63,8 @@ typedef enum {
     B200ALG_CUDA_ERROR = 4,         /* see b200alg_last_cuda_error() */
     B200ALG_WAIT_LIMIT = 5,         /* a device-side wait ran out (reported by b200alg_device_status) */
     B200ALG_MISALIGNED = 6,         /* a pointer is not aligned to its element size / temp not to 256 */
-    B200ALG_TOO_LARGE = 7           /* n beyond INT32_MAX (ErrorMessages.NotSupportedArrayView64) */
+    B200ALG_TOO_LARGE = 7,          /* n beyond INT32_MAX (ErrorMessages.NotSupportedArrayView64) */
+    B200ALG_STATIC_LIMIT = 8        /* n beyond what an entry point with built-in scratch accepts */
 } b200alg_status;
 
 int b200alg_version(void);
@@ -117,6 +118,21 @@ int b200alg_scan(void *stream, const void *in, int64_t in_stride, void *out, int
 int b200alg_scan_carry(void *stream, const void *in, int64_t in_stride, void *out, int64_t out_stride,
                        int64_t n, int dtype, int op, int inclusive, const void *carry_in,
                        void *temp, int64_t temp_bytes);
+
+/* Scan for callers that cannot hand over a temp view.  No counterpart in the reference:
+ * there every scan takes (or, through ScanProvider, owns) a temp buffer.  This variant is
+ * for code that gets an input and an output view and has no way to allocate - a stream
+ * callback, a loop that must not touch the allocator, a host that forbids cudaMalloc after
+ * start-up.  The tile descriptors live in an array built into the library (about 768 KiB
+ * of device memory on every GPU that loads it, held until the process exits), which
+ * limits n to 2^26 elements (B200ALG_STATIC_LIMIT beyond that).  The call allocates
+ * nothing.  The first call on each device looks up the array's device address; make that
+ * first call outside any stream capture.  All calls on one device share the array: two
+ * calls whose kernels may overlap on the GPU (different streams) corrupt each other;
+ * calls on the same stream are fine, each one clears what it uses. */
+#define B200ALG_SCAN_STATIC_MAX_ELEMENTS (1ll << 26)
+int b200alg_scan_static(void *stream, const void *in, int64_t in_stride, void *out, int64_t out_stride,
+                        int64_t n, int dtype, int op, int inclusive);
 
 /* ---- reduce -----------------------------------------------------------------------
  * Replaces the lambda of CreateReduction (ReductionExtensions.cs:135-167): out[0] is set

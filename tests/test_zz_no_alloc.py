@@ -1,0 +1,69 @@
+"""The scan entry point that brings its own scratch (for callers that cannot allocate a
+temp view: stream callbacks, allocator-free loops, hosts that forbid cudaMalloc after
+start-up) must give exactly what the regular entry point gives.  Both are called through
+the C ABI, twice in a row, because the second call finds the first one's leftovers in the
+shared scratch array.  Collected last on purpose (file name), and self-contained so that
+it also passes alone in a fresh process."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from ilgpu_b200 import _native as N
+
+pytestmark = pytest.mark.gpu
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _scan_regular(L, stream, src, dtype, op, inclusive):
+    n = src.numel()
+    out = torch.empty_like(src)
+    need = ctypes.c_int64(0)
+    assert L.b200alg_scan_temp_bytes(dtype, n, ctypes.byref(need)) == N.OK
+    temp = torch.empty(need.value // 4 + 64, dtype=torch.int32, device="cuda")
+    assert L.b200alg_scan(stream, _ptr(src), 1, _ptr(out), 1, n, dtype, op, inclusive, _ptr(temp), temp.numel() * 4) == N.OK
+    return out
+
+
+def _scan_static(L, stream, src, dtype, op, inclusive):
+    out = torch.empty_like(src)
+    assert L.b200alg_scan_static(stream, _ptr(src), 1, _ptr(out), 1, src.numel(), dtype, op, inclusive) == N.OK
+    return out
+
+
+def test_static_scratch_scan_matches_regular_scan_twice_in_a_row():
+    L = N.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rng = np.random.default_rng(2024)
+    cases = [
+        (rng.integers(-1000, 1000, size=1_000_003).astype(np.int32), N.I32, N.ADD, 0),   # long: many tiles
+        (rng.integers(0, 2 ** 62, size=70_001).astype(np.int64), N.I64, N.MAX, 1),       # short: reuses dirty scratch
+        (rng.random(300_000).astype(np.float32), N.F32, N.ADD, 1),
+    ]
+    for host, dtype, op, inclusive in cases:
+        src = torch.from_numpy(host).cuda()
+        expected = _scan_regular(L, stream, src, dtype, op, inclusive)
+        first = _scan_static(L, stream, src, dtype, op, inclusive)
+        second = _scan_static(L, stream, src, dtype, op, inclusive)
+        torch.cuda.synchronize()
+        if host.dtype.kind == "f":
+            # float add: the same bound as the other scan tests (the look-back grouping may differ per run)
+            tol = 1e-5 * np.log2(host.size) * float(np.abs(host.astype(np.float64)).sum())
+            for got in (first, second):
+                assert float((got.double() - expected.double()).abs().max()) <= tol
+        else:
+            assert torch.equal(first, expected)
+            assert torch.equal(second, expected)
+
+
+def test_static_scratch_scan_rejects_sizes_beyond_its_limit():
+    L = N.lib()
+    one = torch.zeros(1, dtype=torch.int32, device="cuda")
+    too_many = (1 << 26) + 1
+    rc = L.b200alg_scan_static(None, _ptr(one), 1, _ptr(one), 1, too_many, N.I32, N.ADD, 1)
+    assert rc == N.STATIC_LIMIT
+    assert "scratch" in N.status_string(rc)
