@@ -1,0 +1,287 @@
+"""Radix sort, scan, reduce and histogram over the GPUs of one box.
+
+One process per GPU.  Each primitive shards the data, does its local work through the
+native library, and uses ``torch.distributed`` only for the exchange step the primitive
+really has:
+
+* reduce, histogram - local kernel, then an all-reduce of one element / of the bins;
+* scan - local reduce, all-gather of the per-rank totals, fold of the lower ranks' totals,
+  local scan seeded with that value;
+* sort - sample sort: sampled (key, global index) splitters, stable partition of the shard
+  into one bucket per rank, all-to-all of the buckets, stable local radix sort.  Rank r
+  ends up with the r-th slice of the globally sorted sequence.
+
+The reference has no multi-device algorithms (its only multi-GPU facility is peer access,
+Src/ILGPU/Runtime/PeerAccess.cs), so this is new surface.  The local work goes through a
+small "engine" interface; the product engine is :class:`NativeEngine` (CUDA).  Tests of
+the host logic substitute a CPU engine and run the same code over ``gloo``.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _native as N
+from .algorithms import (Accelerator, B200AlgException, NotSupportedException, RadixSortOperation, ScanKind,
+                         ScanReduceOperation, _ptr, _stream_ptr, dtype_code)
+
+_SIGNED_VIEW = {1: torch.int8, 2: torch.int16, 4: torch.int32, 8: torch.int64}
+_UNSIGNED = (torch.uint8, torch.uint16, torch.uint32, torch.uint64)
+
+
+def _signed_view(t: torch.Tensor) -> torch.Tensor:
+    """Same bits as a signed integer tensor (collectives and indexing know these types)."""
+    target = _SIGNED_VIEW[t.dtype.itemsize]
+    return t if t.dtype == target else t.view(target)
+
+
+class NativeEngine:
+    """Local work on one B200 through the C ABI."""
+
+    def __init__(self, accelerator: Accelerator):
+        self.acc = accelerator
+        self.device = accelerator.device
+        self._temps: dict[str, torch.Tensor] = {}
+
+    def _temp(self, tag: str, ints: int) -> torch.Tensor:
+        t = self._temps.get(tag)
+        if t is None or t.numel() < ints:
+            t = self.acc.Allocate1D(max(ints, 64), torch.int32)
+            self._temps[tag] = t
+        return t
+
+    def empty(self, n: int, dtype: torch.dtype) -> torch.Tensor:
+        return torch.empty(int(n), dtype=dtype, device=self.device)
+
+    def reduce(self, view: torch.Tensor, op: ScanReduceOperation) -> torch.Tensor:
+        out = self.empty(1, op.dtype)
+        self.acc.CreateReduction(op)(None, view, out)
+        return out
+
+    def scan(self, src, dst, op: ScanReduceOperation, kind: ScanKind, carry) -> None:
+        temp = self._temp("scan", self.acc.ComputeScanTempStorageSize(op.dtype, src.numel()))
+        self.acc.CreateScan(op, kind)(None, src, dst, temp, carry_in=carry)
+
+    def histogram(self, view, bins, overflow, locator) -> None:
+        self.acc.CreateHistogram(locator, checked=overflow is not None)(None, view, bins, overflow)
+
+    def sort(self, keys, values, op: RadixSortOperation) -> None:
+        n = keys.numel()
+        if values is None:
+            temp = self._temp("sort", self.acc.ComputeRadixSortTempStorageSize(op, n))
+            self.acc.CreateRadixSort(op)(None, keys, temp)
+        else:
+            temp = self._temp("sort", self.acc.ComputeRadixSortPairsTempStorageSize(op, values.dtype, n))
+            self.acc.CreateRadixSortPairs(op)(None, keys, values, temp)
+
+    def partition(self, keys, values, op: RadixSortOperation, splitter_keys, splitter_index, index_base: int):
+        n = keys.numel()
+        L = self.acc.L
+        need = ctypes.c_int64(0)
+        B200AlgException.ThrowIfFailed(L.b200alg_bucket_partition_temp_bytes(dtype_code(keys.dtype), n, ctypes.byref(need)))
+        temp = self._temp("partition", (need.value + 3) // 4)
+        out_keys = torch.empty_like(keys)
+        out_values = None if values is None else torch.empty_like(values)
+        num_splitters = splitter_keys.numel()
+        counts = self.empty(num_splitters + 1, torch.int64)
+        with self.acc.Bind():
+            B200AlgException.ThrowIfFailed(L.b200alg_bucket_partition(
+                _stream_ptr(None), _ptr(keys), _ptr(values), n, dtype_code(keys.dtype),
+                0 if values is None else values.dtype.itemsize, N.SORT_DESCENDING if op.descending else 0,
+                _ptr(splitter_keys), _ptr(splitter_index), num_splitters, int(index_base),
+                _ptr(out_keys), _ptr(out_values), _ptr(counts), _ptr(temp), temp.numel() * 4))
+        return out_keys, out_values, counts
+
+
+def _identity_tensor(op: ScanReduceOperation, device) -> torch.Tensor:
+    """One element holding the operation's Identity (0, MinValue or MaxValue)."""
+    dt = op.dtype
+    if op.op == N.ADD:
+        return torch.zeros(1, dtype=_SIGNED_VIEW[dt.itemsize] if dt in _UNSIGNED else dt, device=device).view(dt)
+    if dt.is_floating_point:
+        info = torch.finfo(dt)
+        return torch.full((1,), info.min if op.op == N.MAX else info.max, dtype=dt, device=device)
+    if dt in _UNSIGNED:   # MinValue = all zero bits, MaxValue = all one bits
+        return torch.full((1,), 0 if op.op == N.MAX else -1, dtype=_SIGNED_VIEW[dt.itemsize], device=device).view(dt)
+    info = torch.iinfo(dt)
+    return torch.full((1,), info.min if op.op == N.MAX else info.max, dtype=dt, device=device)
+
+
+def _fold_lower_ranks(totals: torch.Tensor, rank: int, op: ScanReduceOperation) -> torch.Tensor | None:
+    """Combines the totals of ranks < rank in rank order; None for rank 0 (= Identity)."""
+    if rank == 0:
+        return None
+    lower = totals[:rank]
+    dt = op.dtype
+    if op.op == N.ADD:
+        if dt.is_floating_point:
+            return lower.to(torch.float64).sum().to(dt).reshape(1)
+        s = _signed_view(lower).to(torch.int64).sum()          # wraps like unchecked C# arithmetic
+        if dt.itemsize == 4:
+            s = ((s + 2 ** 31) % 2 ** 32) - 2 ** 31
+        return s.to(_SIGNED_VIEW[dt.itemsize]).reshape(1).view(dt)
+    pick = torch.max if op.op == N.MAX else torch.min
+    if dt in _UNSIGNED:
+        flip = -(2 ** (dt.itemsize * 8 - 1))
+        return (pick(_signed_view(lower) ^ flip) ^ flip).reshape(1).view(dt)
+    return pick(lower).reshape(1)
+
+
+class ShardedAlgorithms:
+    """The primitives over all ranks of a process group (one rank per GPU)."""
+
+    SAMPLES_PER_RANK = 2048
+
+    def __init__(self, engine, group=None):
+        self.engine = NativeEngine(engine) if isinstance(engine, Accelerator) else engine
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+
+    # -- collectives on bit patterns --
+    def _all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        s = _signed_view(t.contiguous())
+        parts = [torch.empty_like(s) for _ in range(self.world)]
+        dist.all_gather(parts, s, group=self.group)
+        return torch.cat(parts).view(t.dtype)
+
+    def _all_reduce(self, t: torch.Tensor, op_code: int) -> None:
+        if op_code == N.ADD:
+            dist.all_reduce(t if t.dtype.is_floating_point else _signed_view(t), op=dist.ReduceOp.SUM, group=self.group)
+            return
+        red = dist.ReduceOp.MAX if op_code == N.MAX else dist.ReduceOp.MIN
+        if t.dtype in _UNSIGNED:
+            s = _signed_view(t)
+            flip = -(2 ** (t.dtype.itemsize * 8 - 1))
+            s ^= flip
+            dist.all_reduce(s, op=red, group=self.group)
+            s ^= flip
+        else:
+            dist.all_reduce(t, op=red, group=self.group)
+
+    # -- reduce --
+    def Reduce(self, view: torch.Tensor, operation: ScanReduceOperation) -> torch.Tensor:
+        """Every rank gets the fold over all shards (one element)."""
+        out = self.engine.reduce(view, operation)
+        self._all_reduce(out, operation.op)
+        return out
+
+    # -- histogram --
+    def Histogram(self, view, histogram, histogramOverflow, locator) -> None:
+        """Adds the counts of all shards to every rank's ``histogram`` (replicas must agree
+        on entry); ``histogramOverflow`` may be None (unchecked)."""
+        local = torch.zeros_like(histogram)
+        self.engine.histogram(view, local, None, locator)
+        self._all_reduce(local, N.ADD)
+        if histogramOverflow is not None and not histogram.dtype.is_floating_point:
+            # an increment started from MaxValue iff the distance up to MaxValue is below the count
+            bits = histogram.dtype.itemsize * 8
+            h, c = _signed_view(histogram).to(torch.int64), _signed_view(local).to(torch.int64)
+            if bits == 32:
+                top = (2 ** 32 - 1) if histogram.dtype in _UNSIGNED else (2 ** 31 - 1)
+                dist_to_max = (top - h) % 2 ** 32
+                crossed = dist_to_max < (c % 2 ** 32)
+            else:
+                # 64-bit bins: compare in the unsigned order via the sign-flip trick
+                top = -1 if histogram.dtype in _UNSIGNED else (2 ** 63 - 1)
+                flip = -(2 ** 63)
+                crossed = ((top - h) ^ flip) < (c ^ flip)
+            histogramOverflow |= crossed.any().to(histogramOverflow.dtype)
+        sh, sl = (histogram, local) if histogram.dtype.is_floating_point else (_signed_view(histogram), _signed_view(local))
+        sh += sl
+
+    # -- scan --
+    def Scan(self, input: torch.Tensor, output: torch.Tensor, operation: ScanReduceOperation, kind: ScanKind) -> None:
+        """Scan of the concatenation of all ranks' inputs (rank order); each rank writes its slice."""
+        if input.numel() == 0:
+            total = _identity_tensor(operation, input.device)
+        else:
+            total = self.engine.reduce(input, operation)
+        totals = self._all_gather(total)
+        carry = _fold_lower_ranks(totals, self.rank, operation)
+        if input.numel():
+            self.engine.scan(input, output, operation, kind, carry)
+
+    # -- sort --
+    def _sort(self, keys: torch.Tensor, values: torch.Tensor | None, operation: RadixSortOperation):
+        eng, G, r = self.engine, self.world, self.rank
+        n = keys.numel()
+        device = keys.device
+        counts_all = self._all_gather(torch.tensor([n], dtype=torch.int64, device=device)).tolist()
+        base = sum(counts_all[:r])
+        total = sum(counts_all)
+        if total == 0:
+            return keys, values
+
+        # 1. samples: evenly spaced (key, global index) pairs of this shard
+        s = self.SAMPLES_PER_RANK
+        pos = (torch.arange(s, dtype=torch.int64, device=device) * n) // s if n else torch.zeros(0, dtype=torch.int64, device=device)
+        if n:
+            sample_keys = _signed_view(keys)[pos].view(keys.dtype)
+            sample_index = pos + base
+        else:
+            sample_keys, sample_index = keys[:0], pos
+        # ranks without data contribute copies of nothing: pad to s so that all_gather is regular
+        pad = s - sample_keys.numel()
+        valid = torch.ones(s, dtype=torch.int64, device=device)
+        if pad:
+            sample_keys = torch.cat([sample_keys, torch.zeros(pad, dtype=_SIGNED_VIEW[keys.dtype.itemsize], device=device).view(keys.dtype)])
+            sample_index = torch.cat([sample_index, torch.zeros(pad, dtype=torch.int64, device=device)])
+            valid[s - pad:] = 0
+        all_keys = self._all_gather(sample_keys)
+        all_index = self._all_gather(sample_index)
+        all_valid = self._all_gather(valid).bool()
+        all_keys = _signed_view(all_keys)[all_valid].view(keys.dtype).contiguous()
+        all_index = all_index[all_valid].contiguous()
+        # gathered in rank order, so indices ascend: a stable sort by key orders the pairs
+        eng.sort(all_keys, all_index, operation)
+        m = all_keys.numel()
+        cut = (torch.arange(1, G, dtype=torch.int64, device=device) * m) // G
+        splitter_keys = _signed_view(all_keys)[cut].view(keys.dtype).contiguous()
+        splitter_index = all_index[cut].contiguous()
+
+        # 2. stable partition of the shard into one bucket per rank
+        if n:
+            out_keys, out_values, counts = eng.partition(keys, values, operation, splitter_keys, splitter_index, base)
+        else:
+            out_keys, out_values, counts = keys, values, torch.zeros(G, dtype=torch.int64, device=device)
+
+        # 3. exchange
+        matrix = self._all_gather(counts).view(G, G).tolist()      # matrix[src][dst]
+        send = [int(c) for c in matrix[r]]
+        recv = [int(matrix[src][r]) for src in range(G)]
+        recv_keys = eng.empty(sum(recv), keys.dtype)
+        dist.all_to_all_single(_signed_view(recv_keys), _signed_view(out_keys), recv, send, group=self.group)
+        recv_values = None
+        if values is not None:
+            recv_values = eng.empty(sum(recv), values.dtype)
+            dist.all_to_all_single(_signed_view(recv_values), _signed_view(out_values), recv, send, group=self.group)
+
+        # 4. received runs lie in source-rank order; a stable local sort finishes the job
+        if recv_keys.numel():
+            eng.sort(recv_keys, recv_values, operation)
+        return recv_keys, recv_values
+
+    def SortKeys(self, keys: torch.Tensor, operation: RadixSortOperation):
+        """Returns ``(sorted_slice, count)``: rank r holds the r-th slice of the sorted whole."""
+        if keys.dtype != operation.dtype:
+            raise NotSupportedException(f"keys are {keys.dtype}, operation sorts {operation.dtype}")
+        out, _ = self._sort(keys, None, operation)
+        return out, out.numel()
+
+    def SortPairs(self, keys: torch.Tensor, values: torch.Tensor, operation: RadixSortOperation):
+        """Stable: equal keys keep the order (rank, position) they had on entry."""
+        if keys.dtype != operation.dtype:
+            raise NotSupportedException(f"keys are {keys.dtype}, operation sorts {operation.dtype}")
+        if values.dtype.itemsize not in (4, 8):
+            raise NotSupportedException("values of 4 or 8 bytes")
+        return self._sort(keys, values, operation)
+
+    def sort_launches_per_step(self, operation: RadixSortOperation) -> int:
+        """Kernels of the library launched by one SortKeys call: the sample sort and the final
+        sort (histogram, offsets, one pass per key byte, copy-back each) and the partition
+        (bucket histogram, offsets, count export, one pass)."""
+        passes = operation.dtype.itemsize
+        return 2 * (3 + passes) + 4
