@@ -248,12 +248,12 @@ def run_native(args) -> None:
         from ilgpu_b200.multi_gpu import ShardedAlgorithms
         sharded = ShardedAlgorithms(acc, dist.group.WORLD)
         bufs = [pristine.clone() for _ in range(nbuf)]
-        results = [None] * nbuf
+        last = [None]
 
         def step_fn(i):
-            results[i] = sharded.SortKeys(bufs[i], op)
+            last[0] = sharded.SortKeys(bufs[i], op)   # the previous step's output goes back to the allocator
         launches_per_step = sharded.sort_launches_per_step(op)
-        result_of = lambda i: results[i][0]
+        result_of = lambda i: last[0][0]
 
     for i in range(warmup):
         step_fn(i)

@@ -192,12 +192,22 @@ template <typename K> struct SplitterBucket {
     const int64_t *splitter_index;
     int num_splitters;
     int64_t index_base;
+    // Copies the splitters into shared memory (keys already transformed) and reads them from
+    // there afterwards.  Call with all threads of the block, then synchronise.
+    __device__ __forceinline__ void stage(K *shared_keys, int64_t *shared_index) {
+        for (int s = threadIdx.x; s < num_splitters; s += blockDim.x) {
+            shared_keys[s] = xf(splitter_keys[s]);
+            shared_index[s] = splitter_index[s];
+        }
+        splitter_keys = shared_keys;
+        splitter_index = shared_index;
+    }
     __device__ __forceinline__ unsigned int operator()(K key, int64_t local_index) const {
         const K tk = xf(key);
         const int64_t gi = index_base + local_index;
         unsigned int b = 0;
         for (int s = 0; s < num_splitters; ++s) {
-            const K sk = xf(splitter_keys[s]);
+            const K sk = splitter_keys[s];
             b += (sk < tk) || (sk == tk && splitter_index[s] <= gi);
         }
         return b;
@@ -228,7 +238,7 @@ struct OnesweepSmem {
     static constexpr int VB = ValueBytes<V>::value;
     static constexpr int STAGE = (int)sizeof(K) > VB ? (int)sizeof(K) : VB;
     static constexpr size_t bytes = (size_t)TILE * STAGE + (size_t)(THREADS / 32) * kRadix * 4 + kRadix * 4 * 2 + 64 +
-                                    (KEEP_DIGITS ? (size_t)TILE : 0);
+                                    (KEEP_DIGITS ? (size_t)TILE + kRadix * 16 : 0);
 };
 
 // One tile of one digit pass.  FAST = the tile is full and both buffers are dense, so no
@@ -426,6 +436,10 @@ onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, 
     unsigned int *misc = warp_cnt + WARPS * kRadix + 2 * kRadix;
 
     const int tid = threadIdx.x;
+    if constexpr (Digit::kUsesIndex) {
+        unsigned char *after_digits = reinterpret_cast<unsigned char *>(misc + 16) + TILE;
+        dg.stage(reinterpret_cast<K *>(after_digits + kRadix * 8), reinterpret_cast<int64_t *>(after_digits));
+    }
     if (tid == 0) misc[0] = atomicAdd(&hdr->reserved[kCtlTicket + pass], 1u);
     for (int i = tid; i < WARPS * kRadix; i += THREADS) warp_cnt[i] = 0u;
     __syncthreads();
@@ -584,6 +598,9 @@ template <typename K>
 __global__ void __launch_bounds__(256)
 bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K> dg, unsigned int *ghist) {
     __shared__ unsigned int sh[8][kRadix];
+    __shared__ K staged_keys[kRadix];
+    __shared__ int64_t staged_index[kRadix];
+    dg.stage(staged_keys, staged_index);
     for (int i = threadIdx.x; i < 8 * kRadix; i += 256) (&sh[0][0])[i] = 0u;
     __syncthreads();
     unsigned int *mine = sh[threadIdx.x >> 5];

@@ -205,40 +205,39 @@ class ShardedAlgorithms:
             self.engine.scan(input, output, operation, kind, carry)
 
     # -- sort --
+    # Global position of element i of rank r, as used for tie-breaking: r * 2^40 + i.  It only
+    # has to be monotone in (rank, position), so no prefix sum of the shard sizes is needed.
+    _RANK_SHIFT = 40
+
     def _sort(self, keys: torch.Tensor, values: torch.Tensor | None, operation: RadixSortOperation):
         eng, G, r = self.engine, self.world, self.rank
         n = keys.numel()
         device = keys.device
-        counts_all = self._all_gather(torch.tensor([n], dtype=torch.int64, device=device)).tolist()
-        base = sum(counts_all[:r])
-        total = sum(counts_all)
-        if total == 0:
-            return keys, values
-
-        # 1. samples: evenly spaced (key, global index) pairs of this shard
         s = self.SAMPLES_PER_RANK
-        pos = (torch.arange(s, dtype=torch.int64, device=device) * n) // s if n else torch.zeros(0, dtype=torch.int64, device=device)
+        kview = _SIGNED_VIEW[keys.dtype.itemsize]
+        base = r << self._RANK_SHIFT
+
+        # 1. samples: evenly spaced (key, global position) pairs of this shard (with repeats
+        #    when the shard is short), gathered together with the shard size in one message
+        msg = torch.zeros(2 * s + 1, dtype=torch.int64, device=device)
+        msg[0] = n
         if n:
-            sample_keys = _signed_view(keys)[pos].view(keys.dtype)
-            sample_index = pos + base
-        else:
-            sample_keys, sample_index = keys[:0], pos
-        # ranks without data contribute copies of nothing: pad to s so that all_gather is regular
-        pad = s - sample_keys.numel()
-        valid = torch.ones(s, dtype=torch.int64, device=device)
-        if pad:
-            sample_keys = torch.cat([sample_keys, torch.zeros(pad, dtype=_SIGNED_VIEW[keys.dtype.itemsize], device=device).view(keys.dtype)])
-            sample_index = torch.cat([sample_index, torch.zeros(pad, dtype=torch.int64, device=device)])
-            valid[s - pad:] = 0
-        all_keys = self._all_gather(sample_keys)
-        all_index = self._all_gather(sample_index)
-        all_valid = self._all_gather(valid).bool()
-        all_keys = _signed_view(all_keys)[all_valid].view(keys.dtype).contiguous()
-        all_index = all_index[all_valid].contiguous()
-        # gathered in rank order, so indices ascend: a stable sort by key orders the pairs
+            pos = (torch.arange(s, dtype=torch.int64, device=device) * n) // s
+            msg[1:1 + s] = _signed_view(keys)[pos].to(torch.int64)
+            msg[1 + s:] = pos + base
+        table = self._all_gather(msg).view(G, 2 * s + 1)
+        sizes = table[:, 0]
+        # a rank without data has no samples: it borrows the block of the first rank that has some
+        has = sizes > 0
+        donor = torch.argmax(has.to(torch.int64))
+        block = torch.where(has, torch.arange(G, device=device), donor)
+        table = table[block]
+        all_keys = table[:, 1:1 + s].reshape(-1).to(kview).view(keys.dtype).contiguous()
+        all_index = table[:, 1 + s:].reshape(-1).contiguous()
+        # blocks lie in rank order and positions ascend inside a block, so a stable sort by key
+        # orders the (key, position) pairs
         eng.sort(all_keys, all_index, operation)
-        m = all_keys.numel()
-        cut = (torch.arange(1, G, dtype=torch.int64, device=device) * m) // G
+        cut = (torch.arange(1, G, dtype=torch.int64, device=device) * (G * s)) // G
         splitter_keys = _signed_view(all_keys)[cut].view(keys.dtype).contiguous()
         splitter_index = all_index[cut].contiguous()
 
@@ -248,7 +247,7 @@ class ShardedAlgorithms:
         else:
             out_keys, out_values, counts = keys, values, torch.zeros(G, dtype=torch.int64, device=device)
 
-        # 3. exchange
+        # 3. exchange (the split sizes have to reach the host: the one synchronisation of the sort)
         matrix = self._all_gather(counts).view(G, G).tolist()      # matrix[src][dst]
         send = [int(c) for c in matrix[r]]
         recv = [int(matrix[src][r]) for src in range(G)]
