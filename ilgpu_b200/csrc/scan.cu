@@ -7,27 +7,49 @@
 
 namespace b200alg {
 
-constexpr int kScanThreads = 256;
+#ifndef B200ALG_SCAN_THREADS
+#define B200ALG_SCAN_THREADS 256
+#endif
+#ifndef B200ALG_SCAN_VEC
+#define B200ALG_SCAN_VEC 8
+#endif
+#ifndef B200ALG_SCAN_MIN_BLOCKS
+#define B200ALG_SCAN_MIN_BLOCKS 1
+#endif
+constexpr int kScanThreads = B200ALG_SCAN_THREADS;
 constexpr int kScanWarps = kScanThreads / 32;
-constexpr int kScanVecPerThread = 4;  // 4 x 16 bytes per thread -> 16 KB per tile
+constexpr int kScanVecPerThread = B200ALG_SCAN_VEC;  // 8 x 16 bytes per thread -> 32 KB per tile
+
+constexpr int kScanMinTileElems = 2 * kScanVecPerThread * kScanThreads;  // tile of an 8-byte type
 
 enum : unsigned int { kInvalid = 0u, kAggregate = 1u, kInclusive = 2u };
 
-// Tile descriptors.  4-byte types pack {flag, value} into one 64-bit word that is read
-// and written with single (relaxed) accesses.  8-byte types keep the two partial results
-// in separate slots and publish the flag with release / acquire.
+// Tile descriptors, one record of kDescStride bytes per tile.  Records are spread out so that
+// the polls of many successor tiles do not all land on one L2 line.  4-byte types pack
+// {flag, value} into one 64-bit word that is read and written with single (relaxed)
+// accesses.  8-byte types keep the two partial results in separate slots of the record and
+// publish the flag with release / acquire.
+#ifndef B200ALG_SCAN_DESC_STRIDE
+#define B200ALG_SCAN_DESC_STRIDE 128
+#endif
+constexpr int kDescStride = B200ALG_SCAN_DESC_STRIDE;
+static_assert(kDescStride >= 32 && kDescStride % 32 == 0, "a record holds flag + two 8-byte values");
+
 template <typename T, int BYTES = sizeof(T)> struct TileState;
 
 template <typename T> struct TileState<T, 4> {
-    unsigned long long *words;
-    __host__ __device__ TileState(void *base, int) : words((unsigned long long *)base) {}
+    unsigned char *base;
+    __host__ __device__ TileState(void *b, int) : base((unsigned char *)b) {}
+    __device__ __forceinline__ unsigned long long *word(int tile) const {
+        return (unsigned long long *)(base + (size_t)tile * kDescStride);
+    }
     __device__ __forceinline__ void publish(int tile, unsigned int flag, T v) {
         unsigned int bits;
         memcpy(&bits, &v, 4);
-        st_relaxed_u64(words + tile, ((unsigned long long)flag << 32) | bits);
+        st_relaxed_u64(word(tile), ((unsigned long long)flag << 32) | bits);
     }
     __device__ __forceinline__ unsigned int poll(int tile, T &v) {
-        unsigned long long w = ld_relaxed_u64(words + tile);
+        unsigned long long w = ld_relaxed_u64(word(tile));
         unsigned int bits = (unsigned int)w;
         memcpy(&v, &bits, 4);
         return (unsigned int)(w >> 32);
@@ -35,25 +57,20 @@ template <typename T> struct TileState<T, 4> {
 };
 
 template <typename T> struct TileState<T, 8> {
-    unsigned int *flags;
-    T *agg;
-    T *incl;
-    __host__ __device__ TileState(void *base, int tiles) {
-        agg = (T *)base;
-        incl = agg + tiles;
-        flags = (unsigned int *)(incl + tiles);
-    }
+    unsigned char *base;   // record: flag (4 bytes) at 0, aggregate at 8, inclusive at 16
+    __host__ __device__ TileState(void *b, int) : base((unsigned char *)b) {}
     __device__ __forceinline__ void publish(int tile, unsigned int flag, T v) {
-        T *slot = (flag == kInclusive ? incl : agg) + tile;
+        unsigned char *rec = base + (size_t)tile * kDescStride;
         unsigned long long bits;
         memcpy(&bits, &v, 8);
-        st_relaxed_u64((unsigned long long *)slot, bits);
-        st_release_u32(flags + tile, flag);
+        st_relaxed_u64((unsigned long long *)(rec + (flag == kInclusive ? 16 : 8)), bits);
+        st_release_u32((unsigned int *)rec, flag);
     }
     __device__ __forceinline__ unsigned int poll(int tile, T &v) {
-        unsigned int f = ld_acquire_u32(flags + tile);
+        unsigned char *rec = base + (size_t)tile * kDescStride;
+        unsigned int f = ld_acquire_u32((const unsigned int *)rec);
         if (f != kInvalid) {
-            unsigned long long bits = ld_relaxed_u64((const unsigned long long *)((f == kInclusive ? incl : agg) + tile));
+            unsigned long long bits = ld_relaxed_u64((const unsigned long long *)(rec + (f == kInclusive ? 16 : 8)));
             memcpy(&v, &bits, 8);
         }
         return f;
@@ -63,7 +80,7 @@ template <typename T> struct TileState<T, 8> {
 __device__ __forceinline__ int swz(int slot) { return slot ^ ((slot >> 3) & 7); }
 
 template <typename T, int OP, bool INCLUSIVE, bool VECTOR>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kScanThreads, B200ALG_SCAN_MIN_BLOCKS)
 scan_kernel(const T *in, int64_t in_stride, T *out, int64_t out_stride, int64_t n, const T *carry_in,
             TempHeader *hdr, void *state_base, int num_tiles) {
     using O = Op<T, OP>;
@@ -209,14 +226,276 @@ scan_kernel(const T *in, int64_t in_stride, T *out, int64_t out_stride, int64_t 
     }
 }
 
+// ---- pipelined variant for dense, 16-byte aligned views ---------------------------------
+// Persistent blocks take tiles round-robin (tile = blockIdx.x + k * gridDim.x); all blocks
+// of the grid are resident at once, so a tile only ever waits for tiles that already run.
+// The input of the next tiles is staged into a shared-memory ring by bulk asynchronous
+// copies (TMA, one elected thread, completion on an mbarrier), which keeps loads in flight
+// while a block is busy with the scan and the look-back of its current tile.
+#ifndef B200ALG_SCAN_STAGES
+#define B200ALG_SCAN_STAGES 2
+#endif
+constexpr int kScanStages = B200ALG_SCAN_STAGES;
+constexpr int kScanTileBytes = kScanThreads * kScanVecPerThread * 16;
+constexpr unsigned int kMaxBarrierPolls = 1u << 22;
+
+__device__ __forceinline__ unsigned int smem_addr(const void *p) { return (unsigned int)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned int parity) {
+    unsigned int ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bulk copy global -> this block's shared memory (no multicast); both addresses and the size
+// are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, unsigned int bytes, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned int parity) {
+    for (unsigned int polls = 0; polls < kMaxBarrierPolls; ++polls)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+template <typename T, int OP, bool INCLUSIVE>
+__global__ void __launch_bounds__(kScanThreads)
+scan_pipeline_kernel(const T *in, T *out, int64_t n, const T *carry_in, TempHeader *hdr, void *state_base, int num_tiles) {
+    using O = Op<T, OP>;
+    constexpr int VEC = 16 / sizeof(T);
+    constexpr int NV = kScanVecPerThread;
+    constexpr int TILE = VEC * NV * kScanThreads;
+    union Vec { uint4 u; T t[VEC]; };
+
+    extern __shared__ __align__(128) unsigned char ring[];  // kScanStages x kScanTileBytes
+    __shared__ __align__(8) unsigned long long full_bar[kScanStages];
+    __shared__ T warp_total[kScanWarps];
+    __shared__ T warp_excl[kScanWarps];
+    __shared__ T s_prefix;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = (int)gridDim.x;
+    const int full_tiles = (int)(n / TILE);  // tiles below this index are complete
+
+    if (tid == 0) {
+        for (int st = 0; st < kScanStages; ++st) mbar_init(&full_bar[st], 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    unsigned int in_flight = 0;  // thread 0: bit st set = a copy into stage st has not been waited for
+    if (tid == 0) {
+        for (int st = 0; st < kScanStages; ++st) {
+            const int t = (int)blockIdx.x + st * G;
+            if (t < full_tiles) {
+                mbar_expect_tx(&full_bar[st], kScanTileBytes);
+                bulk_load(ring + st * kScanTileBytes, in + (int64_t)t * TILE, kScanTileBytes, &full_bar[st]);
+                in_flight |= 1u << st;
+            }
+        }
+    }
+    bool failed = false;
+    TileState<T> state(state_base, num_tiles);
+
+    int k = 0;
+    for (int tile = (int)blockIdx.x; tile < num_tiles; tile += G, ++k) {
+        const int st = k % kScanStages;
+        const unsigned int parity = (unsigned int)(k / kScanStages) & 1u;
+        const int64_t base = (int64_t)tile * TILE;
+        const bool full = tile < full_tiles;
+
+        // Vector j of lane l covers elements (warp*32*NV + j*32 + l) * VEC ... + VEC of the tile.
+        Vec v[NV];
+        if (full) {
+            if (!mbar_wait(&full_bar[st], parity)) failed = true;
+            const uint4 *src = reinterpret_cast<const uint4 *>(ring + st * kScanTileBytes) + warp * (32 * NV);
+#pragma unroll
+            for (int j = 0; j < NV; ++j) v[j].u = src[j * 32 + lane];
+            if (tid == 0) in_flight &= ~(1u << st);
+        } else {
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    const int64_t idx = base + (int64_t)(warp * (32 * NV) + j * 32 + lane) * VEC + e;
+                    v[j].t[e] = idx < n ? in[idx] : O::identity();
+                }
+        }
+
+        // inclusive scan inside each vector, then NV interleaved warp scans of the vector totals
+        T w[NV];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+#pragma unroll
+            for (int e = 1; e < VEC; ++e) v[j].t[e] = O::apply(v[j].t[e - 1], v[j].t[e]);
+            w[j] = v[j].t[VEC - 1];
+        }
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const T up = shfl_up(w[j], d);
+                if (lane >= d) w[j] = O::apply(up, w[j]);
+            }
+        }
+        T before[NV];  // fold of everything in the warp's chunk that precedes vector j of this lane
+        T chunk = O::identity();
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            T ex = shfl_up(w[j], 1);
+            if (lane == 0) ex = O::identity();
+            before[j] = O::apply(chunk, ex);
+            chunk = O::apply(chunk, shfl_idx(w[j], 31));
+        }
+        if (lane == 31) warp_total[warp] = chunk;
+        __syncthreads();  // warp totals are visible; every thread has taken its data out of the ring
+
+        if (tid == 0 && !failed) {
+            const int t2 = tile + kScanStages * G;
+            if (t2 < full_tiles) {
+                mbar_expect_tx(&full_bar[st], kScanTileBytes);
+                bulk_load(ring + st * kScanTileBytes, in + (int64_t)t2 * TILE, kScanTileBytes, &full_bar[st]);
+                in_flight |= 1u << st;
+            }
+        }
+
+        if (warp == 0) {
+            T wt = lane < kScanWarps ? warp_total[lane] : O::identity();
+            T wi = wt;
+#pragma unroll
+            for (int d = 1; d < kScanWarps; d <<= 1) {
+                T up = shfl_up(wi, d);
+                if (lane >= d) wi = O::apply(up, wi);
+            }
+            T we = shfl_up(wi, 1);
+            if (lane == 0) we = O::identity();
+            if (lane < kScanWarps) warp_excl[lane] = we;
+            const T aggregate = shfl_idx(wi, kScanWarps - 1);
+
+            T prefix;
+            if (tile == 0) {
+                prefix = carry_in ? *carry_in : O::identity();
+                if (lane == 0) state.publish(0, kInclusive, O::apply(prefix, aggregate));
+            } else {
+                if (lane == 0) state.publish(tile, kAggregate, aggregate);
+                // Decoupled look-back over kLookWays * 32 predecessors per round: lane l polls
+                // the tiles at distances l+1, l+33, ... so that several loads are in flight per
+                // lane; the operations are commutative, so the round's values are simply folded.
+#ifndef B200ALG_SCAN_LOOK_WAYS
+#define B200ALG_SCAN_LOOK_WAYS 1
+#endif
+                constexpr int kLookWays = B200ALG_SCAN_LOOK_WAYS;
+#ifndef B200ALG_SCAN_LOOK_LANES
+#define B200ALG_SCAN_LOOK_LANES 32
+#endif
+                constexpr int kLookLanes = kLookWays > 1 ? 32 : B200ALG_SCAN_LOOK_LANES;
+                prefix = O::identity();
+                int look = tile - 1 - lane;
+                bool gave_up = false;
+                while (true) {
+                    T pv[kLookWays];
+                    unsigned int flag[kLookWays];
+#pragma unroll
+                    for (int m = 0; m < kLookWays; ++m) {
+                        pv[m] = O::identity();
+                        flag[m] = kInclusive;  // tiles before tile 0 act as "inclusive identity"
+                        if (lane >= kLookLanes) flag[m] = kAggregate;  // outside the window: contributes nothing
+                        else if (look - 32 * m >= 0) flag[m] = state.poll(look - 32 * m, pv[m]);
+                    }
+#pragma unroll
+                    for (int m = 0; m < kLookWays; ++m) {
+                        unsigned int spins = 0;
+                        while (flag[m] == kInvalid) {
+                            if (++spins > kMaxSpin) { gave_up = true; flag[m] = kInclusive; pv[m] = O::identity(); break; }
+                            __nanosleep(20);
+                            flag[m] = state.poll(look - 32 * m, pv[m]);
+                        }
+                    }
+                    // nearest predecessor with an inclusive prefix: smallest distance m*32 + lane
+                    int nearest = kLookWays * 32;
+#pragma unroll
+                    for (int m = kLookWays - 1; m >= 0; --m) {
+                        const unsigned int mask = __ballot_sync(0xffffffffu, flag[m] == kInclusive);
+                        if (mask) nearest = m * 32 + (__ffs(mask) - 1);
+                    }
+                    T contrib = O::identity();
+#pragma unroll
+                    for (int m = 0; m < kLookWays; ++m)
+                        if (m * 32 + lane <= nearest) contrib = O::apply(pv[m], contrib);
+#pragma unroll
+                    for (int d = 16; d > 0; d >>= 1) contrib = O::apply(shfl_down(contrib, d), contrib);
+                    prefix = O::apply(shfl_idx(contrib, 0), prefix);
+                    if (nearest < kLookWays * 32) break;
+                    look -= kLookWays > 1 ? kLookWays * 32 : kLookLanes;
+                }
+                if (__any_sync(0xffffffffu, gave_up) && lane == 0) atomicExch(&hdr->wait_limit_hit, 1u);
+                if (lane == 0) state.publish(tile, kInclusive, O::apply(prefix, aggregate));
+            }
+            if (lane == 0) s_prefix = prefix;
+        }
+        __syncthreads();
+
+        const T warp_base = O::apply(s_prefix, warp_excl[warp]);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const T p = O::apply(warp_base, before[j]);
+            if (INCLUSIVE) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) v[j].t[e] = O::apply(p, v[j].t[e]);
+            } else {
+#pragma unroll
+                for (int e = VEC - 1; e > 0; --e) v[j].t[e] = O::apply(p, v[j].t[e - 1]);
+                v[j].t[0] = p;
+            }
+        }
+        if (full) {
+            uint4 *dst = reinterpret_cast<uint4 *>(out + base) + warp * (32 * NV);
+#pragma unroll
+            for (int j = 0; j < NV; ++j) __stcs(dst + j * 32 + lane, v[j].u);
+        } else {
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    const int64_t idx = base + (int64_t)(warp * (32 * NV) + j * 32 + lane) * VEC + e;
+                    if (idx < n) out[idx] = v[j].t[e];
+                }
+        }
+    }
+
+    // A barrier wait that ran out is reported; copies that may still be in flight are given
+    // one more bounded wait so that the block does not retire underneath them.
+    if (__syncthreads_or(failed)) {
+        if (tid == 0) {
+            atomicExch(&hdr->wait_limit_hit, 1u);
+            for (int st = 0; st < kScanStages; ++st)
+                if (in_flight & (1u << st)) {
+                    mbar_wait(&full_bar[st], 0u);
+                    mbar_wait(&full_bar[st], 1u);
+                }
+        }
+    }
+}
+
 template <typename T> constexpr int scan_tile_elems() { return (16 / (int)sizeof(T)) * kScanVecPerThread * kScanThreads; }
 
 static int64_t scan_temp_bytes_for(int dtype, int64_t n) {
-    // Sized for the smaller tile (8-byte types, 2048 elements) and the larger descriptor
-    // (24 bytes per tile) so that one formula covers every type.
-    const int64_t tiles = ceil_div(n < 1 ? 1 : n, 2048);
+    // Sized for the smaller tile (8-byte types) so that one formula covers every type.
+    const int64_t tiles = ceil_div(n < 1 ? 1 : n, kScanMinTileElems);
     (void)dtype;
-    return (int64_t)sizeof(TempHeader) + round_up(tiles * 24, 256);
+    return (int64_t)sizeof(TempHeader) + round_up(tiles * kDescStride, 256);
 }
 
 template <typename T, int OP, bool INCLUSIVE>
@@ -227,12 +506,27 @@ static int launch_scan(cudaStream_t s, const void *in, int64_t in_stride, void *
     const int tiles = (int)tiles64;
     TempHeader *hdr = (TempHeader *)temp;
     void *state = (char *)temp + sizeof(TempHeader);
-    const size_t state_bytes = sizeof(T) == 4 ? (size_t)tiles * 8 : (size_t)tiles * 20;
+    const size_t state_bytes = (size_t)tiles * kDescStride;
     B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, sizeof(TempHeader) + state_bytes, s));
     const bool vec = in_stride == 1 && out_stride == 1 && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    if (vec)
-        scan_kernel<T, OP, INCLUSIVE, true><<<tiles, kScanThreads, 0, s>>>((const T *)in, 1, (T *)out, 1, n, (const T *)carry_in, hdr, state, tiles);
-    else
+    if (vec) {
+        auto kernel = scan_pipeline_kernel<T, OP, INCLUSIVE>;
+        constexpr size_t ring_bytes = (size_t)kScanStages * kScanTileBytes;
+        static thread_local int configured_device = -1;
+        static thread_local int blocks_per_sm = 0;
+        int dev = 0;
+        B200ALG_CUDA_TRY(cudaGetDevice(&dev));
+        if (configured_device != dev) {
+            B200ALG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring_bytes));
+            B200ALG_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, kernel, kScanThreads, ring_bytes));
+            if (blocks_per_sm < 1) return B200ALG_UNSUPPORTED;
+            configured_device = dev;
+        }
+        // every block of the grid must be resident at the same time (tiles are taken round-robin)
+        const int resident = sm_count() * blocks_per_sm;
+        const int blocks = tiles < resident ? tiles : resident;
+        kernel<<<blocks, kScanThreads, ring_bytes, s>>>((const T *)in, (T *)out, n, (const T *)carry_in, hdr, state, tiles);
+    } else
         scan_kernel<T, OP, INCLUSIVE, false><<<tiles, kScanThreads, 0, s>>>((const T *)in, in_stride, (T *)out, out_stride, n, (const T *)carry_in, hdr, state, tiles);
     B200ALG_LAUNCH_CHECK();
     return B200ALG_OK;
@@ -305,7 +599,7 @@ extern "C" int b200alg_scan(void *stream, const void *in, int64_t in_stride, voi
 // else).  For them the tile descriptors of the chained scan live in this fixed array,
 // which every GPU that loads the library carries until the process exits.
 constexpr int64_t kStaticScanMaxElements = 1ll << 26;
-constexpr size_t kStaticScanScratchBytes = sizeof(TempHeader) + (size_t)(kStaticScanMaxElements / 2048) * 24;
+constexpr size_t kStaticScanScratchBytes = sizeof(TempHeader) + (size_t)(kStaticScanMaxElements / kScanMinTileElems) * kDescStride;
 static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScanScratchBytes];
 
 // Device address of the array on the current device.  The array's name is only a handle on

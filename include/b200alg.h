@@ -123,8 +123,8 @@ int b200alg_scan_carry(void *stream, const void *in, int64_t in_stride, void *ou
  * there every scan takes (or, through ScanProvider, owns) a temp buffer.  This variant is
  * for code that gets an input and an output view and has no way to allocate - a stream
  * callback, a loop that must not touch the allocator, a host that forbids cudaMalloc after
- * start-up.  The tile descriptors live in an array built into the library (about 768 KiB
- * of device memory on every GPU that loads it, held until the process exits), which
+ * start-up.  The tile descriptors live in an array built into the library (about 2 MiB of
+ * device memory on every GPU that loads it, held until the process exits), which
  * limits n to 2^26 elements (B200ALG_STATIC_LIMIT beyond that).  The call allocates
  * nothing.  The first call on each device looks up the array's device address; make that
  * first call outside any stream capture.  All calls on one device share the array: two
