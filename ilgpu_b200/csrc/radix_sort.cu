@@ -24,7 +24,7 @@ constexpr int kMaxPasses = 8;
 
 // Control words that live in TempHeader::reserved.
 enum : int {
-    kCtlTicket = 0,        // [0..7]  next tile id of each pass
+    kCtlTicket = 0,        // [0..7]  reserved (tiles are assigned round-robin, no tickets)
     kCtlSkip = 8,          // [8..15] 1 = every key has the same digit at this position
     kCtlSrcIsAlt = 16,     // [16..23] 1 = this pass reads the alternate buffer
     kCtlFinalInAlt = 24    // 1 = the sorted data ended in the alternate buffer
@@ -221,15 +221,15 @@ template <> struct ValueBytes<NoValue> { static constexpr int value = 0; };
 // Lanes of a warp that hold the same 8-bit digit: one ballot per digit bit (the hardware
 // match instruction serialises over the distinct values, ~30 of them for random digits).
 __device__ __forceinline__ unsigned int match_digit(unsigned int digit) {
-    unsigned int peers = 0xffffffffu;
+    unsigned int differs = 0u;  // lanes whose digit differs from this lane's in some bit
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
-        int ext;  // bit b replicated over the word
-        asm("bfe.s32 %0, %1, %2, 1;" : "=r"(ext) : "r"(digit), "r"(b));
-        const unsigned int m = __ballot_sync(0xffffffffu, ext != 0);
-        peers &= ~(m ^ (unsigned int)ext);
+        const bool bit = (digit & (1u << b)) != 0u;
+        const unsigned int m = __ballot_sync(0xffffffffu, bit);
+        const unsigned int ext = bit ? 0xffffffffu : 0u;
+        differs |= m ^ ext;
     }
-    return peers;
+    return ~differs;
 }
 
 template <typename K, typename V, bool KEEP_DIGITS, int THREADS, int ITEMS>
@@ -237,53 +237,120 @@ struct OnesweepSmem {
     static constexpr int TILE = THREADS * ITEMS;
     static constexpr int VB = ValueBytes<V>::value;
     static constexpr int STAGE = (int)sizeof(K) > VB ? (int)sizeof(K) : VB;
-    static constexpr size_t bytes = (size_t)TILE * STAGE + (size_t)(THREADS / 32) * kRadix * 4 + kRadix * 4 * 2 + 64 +
+    static constexpr size_t bytes = (size_t)TILE * STAGE + (size_t)(THREADS / 32) * kRadix * 8 + kRadix * 4 * 2 + 64 +
                                     (KEEP_DIGITS ? (size_t)TILE + kRadix * 16 : 0);
 };
 
-// One tile of one digit pass.  FAST = the tile is full and both buffers are dense, so no
-// bounds checks and no stride arithmetic.
-template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS, bool FAST>
-__device__ __forceinline__ void onesweep_tile(const K *src, int64_t src_stride, K *dst, int64_t dst_stride, const V *vsrc,
-                                              V *vdst, int64_t n, int tile, const Digit &dg, TempHeader *hdr,
-                                              const unsigned int *gbase, SW *status, SW *status_next,
-                                              unsigned char *smem_raw) {
-    constexpr int WARPS = THREADS / 32;
+#ifndef B200ALG_BALLOT_ITEMS
+#define B200ALG_BALLOT_ITEMS 4
+#endif
+#ifndef B200ALG_LOOK_WINDOW
+#define B200ALG_LOOK_WINDOW 1
+#endif
+
+#ifdef B200ALG_EXP_TIMING
+// Experimental builds only: thread 0 of every tile records the global timer at phase borders.
+__device__ unsigned long long *g_exp_debug = nullptr;
+#define B200ALG_STAMP(k)                                                  \
+    do {                                                                  \
+        if (threadIdx.x == 0) {                                           \
+            unsigned long long *dbg = g_exp_debug;                        \
+            unsigned long long t;                                         \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));         \
+            if (dbg) dbg[(size_t)tile * 16 + (k)] = t;                    \
+        }                                                                 \
+    } while (0)
+#define B200ALG_RECORD(k, v)                                              \
+    do {                                                                  \
+        if (threadIdx.x == 0 && g_exp_debug) g_exp_debug[(size_t)tile * 16 + (k)] = (v); \
+    } while (0)
+#define B200ALG_ONESWEEP_MIN_BLOCKS 2
+#else
+#define B200ALG_STAMP(k) do {} while (0)
+#define B200ALG_RECORD(k, v) do {} while (0)
+#define B200ALG_ONESWEEP_MIN_BLOCKS 2
+#endif
+
+// Everything one block needs to know about the pass it works on.
+template <typename K, typename V, typename SW> struct PassContext {
+    const K *src;
+    K *dst;
+    int64_t src_stride, dst_stride;
+    const V *vsrc;
+    V *vdst;
+    int64_t n;
+    int num_tiles;
+    bool dense;
+    TempHeader *hdr;
+    const unsigned int *gbase;
+    SW *status, *status_next;
+};
+
+// Keys of one tile in warp-striped order: item i of lane l is element
+// warp * 32 * ITEMS + i * 32 + l of the tile.
+template <typename K, typename V, typename SW, int THREADS, int ITEMS>
+__device__ __forceinline__ void load_tile_keys(K (&key)[ITEMS], const PassContext<K, V, SW> &c, int tile) {
     constexpr int TILE = THREADS * ITEMS;
-    constexpr bool HAS_VALUES = ValueBytes<V>::value != 0;
-    using S = StatusWord<SW>;
-    using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
-    K *skeys = reinterpret_cast<K *>(smem_raw);
-    unsigned int *warp_cnt = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE);  // [WARPS][256]
-    unsigned int *bin_excl = warp_cnt + WARPS * kRadix;    // digit's first slot inside the tile
-    unsigned int *bin_goff = bin_excl + kRadix;            // global index of slot p is bin_goff[d] + p
-    unsigned int *misc = bin_goff + kRadix;                // [0] tile id, [1..8] warp sums
-    unsigned char *sdigit = reinterpret_cast<unsigned char *>(misc + 16);  // only when digits need the index
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_base = (threadIdx.x >> 5) * 32 * ITEMS + (threadIdx.x & 31);
     const int64_t tile_base = (int64_t)tile * TILE;
-    const int valid = FAST ? TILE : (int)((n - tile_base) < TILE ? (n - tile_base) : TILE);
-
-    // Keys in warp-striped order: item i of lane l is element warp*32*ITEMS + i*32 + l.
-    K key[ITEMS];
-    const int warp_base = warp * 32 * ITEMS + lane;
-    if (FAST) {
-        const K *p = src + tile_base + warp_base;
+    if (c.dense && tile_base + TILE <= c.n) {
+        const K *p = c.src + tile_base + warp_base;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) key[i] = p[i * 32];
     } else {
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
-            const int local = warp_base + i * 32;
-            key[i] = local < valid ? src[(tile_base + local) * src_stride] : K(0);
+            const int64_t idx = tile_base + warp_base + i * 32;
+            key[i] = idx < c.n ? c.src[idx * c.src_stride] : K(0);
         }
     }
+}
 
-    // Ranking inside the warp: keys of one item that share a digit find each other by
-    // ballots; the highest such lane advances the warp's count of that digit.  After the
-    // loop warp_cnt[warp][d] is the warp's number of d-keys.
-    unsigned int *my_cnt = warp_cnt + warp * kRadix;
+// One tile of one digit pass; `key` holds the tile's keys on entry and the keys of
+// `next_tile` (if there is one) on return: they are requested as soon as this tile's keys
+// have moved to shared memory, so the loads are in flight during the look-back and the
+// write-out.  FAST = the tile is full and both buffers are dense (no bounds checks, no
+// stride arithmetic).
+template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS, bool FAST>
+__device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext<K, V, SW> &c, int tile, int next_tile,
+                                              const Digit &dg, unsigned char *smem_raw) {
+    constexpr int WARPS = THREADS / 32;
+    constexpr int TILE = THREADS * ITEMS;
+    constexpr bool HAS_VALUES = ValueBytes<V>::value != 0;
+    constexpr int BALLOT_ITEMS = B200ALG_BALLOT_ITEMS < ITEMS ? B200ALG_BALLOT_ITEMS : ITEMS;
+    constexpr int kLookWindow = B200ALG_LOOK_WINDOW;  // predecessors examined per look-back round
+    using S = StatusWord<SW>;
+    using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
+    K *skeys = reinterpret_cast<K *>(smem_raw);
+    // [WARPS][256] entries {x: count, later offset, of the digit in the warp; y: lanes that hold the digit}
+    uint2 *warp_tbl = reinterpret_cast<uint2 *>(smem_raw + (size_t)TILE * L::STAGE);
+    unsigned int *bin_excl = reinterpret_cast<unsigned int *>(warp_tbl + WARPS * kRadix);  // digit's first slot inside the tile
+    unsigned int *bin_goff = bin_excl + kRadix;            // global index of slot p is bin_goff[d] + p
+    unsigned int *misc = bin_goff + kRadix;                // [1..8] warp sums
+    unsigned char *sdigit = reinterpret_cast<unsigned char *>(misc + 16);  // only when digits need the index
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t tile_base = (int64_t)tile * TILE;
+    const int valid = FAST ? TILE : (int)((c.n - tile_base) < TILE ? (c.n - tile_base) : TILE);
+    const int warp_base = warp * 32 * ITEMS + lane;
+
+    {
+        uint4 *z = reinterpret_cast<uint4 *>(warp_tbl);
+        for (int i = tid; i < WARPS * kRadix / 2; i += THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    B200ALG_STAMP(0);
+
+    // Ranking inside the warp: for every item, the lanes that hold the same digit have to find
+    // each other; the lowest of them advances the warp's count of that digit.  Two methods are
+    // interleaved so that neither the integer pipe nor shared memory saturates:
+    //  - ballots: one vote per digit bit, combined in registers;
+    //  - table:   every lane ORs its bit into the digit's mask in the warp's table and reads
+    //             the mask back after a warp barrier.
+    // After the loop the x fields of the warp's table hold its digit counts.
+    uint2 *my_tbl = warp_tbl + warp * kRadix;
     const unsigned int lt = lanemask_lt();
+    const unsigned int my_bit = 1u << lane;
     unsigned int packed[ITEMS];  // (rank among the warp's keys of that digit) << 8 | digit
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
@@ -294,30 +361,42 @@ __device__ __forceinline__ void onesweep_tile(const K *src, int64_t src_stride, 
             const int local = warp_base + i * 32;
             d = local < valid ? dg(key[i], tile_base + local) : 0xFFu;  // padding ranks behind every real key
         }
-        const unsigned int peers = match_digit(d);
-        const unsigned int before = peers & lt;
-        int leader;  // highest lane among the peers
-        asm("bfind.u32 %0, %1;" : "=r"(leader) : "r"(peers));
-        unsigned int old = 0;
-        if (lane == leader) old = atomicAdd(my_cnt + d, (unsigned int)__popc(peers));
-        old = __shfl_sync(0xffffffffu, old, leader);
-        packed[i] = ((old + __popc(before)) << 8) | d;
+        if ((i * BALLOT_ITEMS) / ITEMS != ((i + 1) * BALLOT_ITEMS) / ITEMS) {  // BALLOT_ITEMS of ITEMS, evenly spread
+            const unsigned int peers = match_digit(d);
+            const unsigned int before = peers & lt;
+            const unsigned int count = my_tbl[d].x;
+            __syncwarp();
+            if (before == 0u) my_tbl[d].x = count + (unsigned int)__popc(peers);
+            packed[i] = ((count + (unsigned int)__popc(before)) << 8) | d;
+            __syncwarp();
+        } else {
+            atomicOr(&my_tbl[d].y, my_bit);
+            __syncwarp();
+            const uint2 e = my_tbl[d];
+            __syncwarp();
+            const unsigned int before = e.y & lt;
+            if (before == 0u) my_tbl[d] = make_uint2(e.x + (unsigned int)__popc(e.y), 0u);
+            packed[i] = ((e.x + (unsigned int)__popc(before)) << 8) | d;
+            __syncwarp();
+        }
     }
+    B200ALG_STAMP(1);
     __syncthreads();
+    B200ALG_STAMP(2);
 
     unsigned int tile_count = 0;
     if (tid < kRadix) {
-        status_next[(size_t)tile * kRadix + tid] = 0;
-        // warp_cnt[w][d] becomes the number of d-keys in the warps before w.
+        c.status_next[(size_t)tile * kRadix + tid] = 0;
+        // the x field of entry [w][d] becomes the number of d-keys in the warps before w
         unsigned int run = 0;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const unsigned int c = warp_cnt[w * kRadix + tid];
-            warp_cnt[w * kRadix + tid] = run;
-            run += c;
+            const unsigned int cnt = warp_tbl[w * kRadix + tid].x;
+            warp_tbl[w * kRadix + tid].x = run;
+            run += cnt;
         }
         tile_count = run;
-        S::st(status + (size_t)tile * kRadix + tid, (tile == 0 ? S::kIncl : S::kAgg) | (SW)tile_count);
+        S::st(c.status + (size_t)tile * kRadix + tid, (tile == 0 ? S::kIncl : S::kAgg) | (SW)tile_count);
         // exclusive scan of the digit counts over the 256 digit threads
         unsigned int incl = tile_count;
 #pragma unroll
@@ -329,6 +408,7 @@ __device__ __forceinline__ void onesweep_tile(const K *src, int64_t src_stride, 
         bin_excl[tid] = incl - tile_count;  // completed below
     }
     __syncthreads();
+    B200ALG_STAMP(3);
     if (tid < kRadix) {
         unsigned int before = 0;
 #pragma unroll
@@ -337,44 +417,78 @@ __device__ __forceinline__ void onesweep_tile(const K *src, int64_t src_stride, 
         bin_excl[tid] = excl;
         // fold the digit's first slot into the per-warp offsets: one table lookup per key
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) warp_cnt[w * kRadix + tid] += excl;
+        for (int w = 0; w < WARPS; ++w) warp_tbl[w * kRadix + tid].x += excl;
     }
     __syncthreads();
+    B200ALG_STAMP(4);
 
     // Scatter through shared memory so that global writes run along digit segments.
     unsigned int pos[ITEMS];
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const unsigned int d = packed[i] & 0xFFu;
-        pos[i] = (packed[i] >> 8) + my_cnt[d];
+        pos[i] = (packed[i] >> 8) + my_tbl[d].x;
         skeys[pos[i]] = key[i];
         if constexpr (Digit::kUsesIndex) sdigit[pos[i]] = (unsigned char)d;
     }
 
-    // Decoupled look-back, one digit per thread.
+    // The registers are free again: request the next tile's keys now.
+    if (next_tile < c.num_tiles) load_tile_keys<K, V, SW, THREADS, ITEMS>(key, c, next_tile);
+    V val[HAS_VALUES ? ITEMS : 1];
+    if constexpr (HAS_VALUES) {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int local = warp_base + i * 32;
+            if (FAST || local < valid) val[i] = c.vsrc[tile_base + local];
+        }
+    }
+    B200ALG_STAMP(5);
+
+    // Decoupled look-back, one digit per thread, kLookWindow predecessors per round (their
+    // loads are independent, so a round costs one trip to L2).
     if (tid < kRadix) {
         unsigned int prefix = 0;
+        unsigned long long steps = 0, polls = 0;
         if (tile > 0) {
-            bool gave_up = false;
-            for (int t = tile - 1; t >= 0; --t) {
-                const SW *slot = status + (size_t)t * kRadix + tid;
-                SW w = S::ld(slot);
-                unsigned int spins = 0;
-                while ((w & ~S::kMask) == 0) {
-                    if (++spins > kMaxSpin) { gave_up = true; break; }
-                    __nanosleep(20);
-                    w = S::ld(slot);
+            bool gave_up = false, done = false;
+            int t = tile - 1;
+            while (!done) {
+                SW window[kLookWindow];
+#pragma unroll
+                for (int k = 0; k < kLookWindow; ++k)
+                    window[k] = t - k >= 0 ? S::ld(c.status + (size_t)(t - k) * kRadix + tid) : (SW)S::kIncl;
+#pragma unroll
+                for (int k = 0; k < kLookWindow; ++k) {
+                    if (!done) {
+                        SW w = window[k];
+                        unsigned int spins = 0;
+                        while ((w & ~S::kMask) == 0) {
+                            if (++spins > kMaxSpin) { gave_up = true; break; }
+                            __nanosleep(20);
+                            w = S::ld(c.status + (size_t)(t - k) * kRadix + tid);
+                        }
+                        polls += spins;
+                        ++steps;
+                        if (gave_up) {
+                            done = true;
+                        } else {
+                            prefix += (unsigned int)(w & S::kMask);
+                            if (w & S::kIncl) done = true;
+                        }
+                    }
                 }
-                if (gave_up) break;
-                prefix += (unsigned int)(w & S::kMask);
-                if (w & S::kIncl) break;
+                t -= kLookWindow;
             }
-            if (gave_up) atomicExch(&hdr->wait_limit_hit, 1u);
-            S::st(status + (size_t)tile * kRadix + tid, S::kIncl | (SW)(prefix + tile_count));
+            if (gave_up) atomicExch(&c.hdr->wait_limit_hit, 1u);
+            S::st(c.status + (size_t)tile * kRadix + tid, S::kIncl | (SW)(prefix + tile_count));
         }
-        bin_goff[tid] = gbase[tid] + prefix - bin_excl[tid];
+        B200ALG_RECORD(10, steps);
+        B200ALG_RECORD(11, polls);
+        bin_goff[tid] = c.gbase[tid] + prefix - bin_excl[tid];
     }
+    B200ALG_STAMP(6);
     __syncthreads();
+    B200ALG_STAMP(7);
 
     unsigned int out_idx[ITEMS];
 #pragma unroll
@@ -385,18 +499,12 @@ __device__ __forceinline__ void onesweep_tile(const K *src, int64_t src_stride, 
             unsigned int d;
             if constexpr (Digit::kUsesIndex) d = sdigit[p]; else d = dg(k, 0);
             out_idx[i] = bin_goff[d] + (unsigned int)p;
-            if (FAST) dst[out_idx[i]] = k; else dst[(int64_t)out_idx[i] * dst_stride] = k;
+            if (FAST) c.dst[out_idx[i]] = k; else c.dst[(int64_t)out_idx[i] * c.dst_stride] = k;
         }
     }
 
     if constexpr (HAS_VALUES) {
         V *svals = reinterpret_cast<V *>(smem_raw);
-        V val[ITEMS];
-#pragma unroll
-        for (int i = 0; i < ITEMS; ++i) {
-            const int local = warp_base + i * 32;
-            if (FAST || local < valid) val[i] = vsrc[tile_base + local];
-        }
         __syncthreads();  // every key has left the staging buffer
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
@@ -407,57 +515,64 @@ __device__ __forceinline__ void onesweep_tile(const K *src, int64_t src_stride, 
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
             const int p = tid + i * THREADS;
-            if (FAST || p < valid) vdst[out_idx[i]] = svals[p];
+            if (FAST || p < valid) c.vdst[out_idx[i]] = svals[p];
         }
     }
+    B200ALG_STAMP(8);
+    __syncthreads();  // staging buffer and tables are reused by the block's next tile
+    B200ALG_STAMP(9);
 }
 
+// Persistent blocks: block b works on tiles b, b + gridDim.x, ...; the grid is sized so that all
+// blocks are resident at once, hence a tile only ever waits for tiles that already run.
 template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, B200ALG_ONESWEEP_MIN_BLOCKS)
 onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, int pass, Digit dg,
                 TempHeader *hdr, const unsigned int *gbase_all, SW *status_all, int num_tiles) {
-    constexpr int WARPS = THREADS / 32;
     constexpr int TILE = THREADS * ITEMS;
     static_assert(THREADS >= kRadix, "one thread per digit");
     using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
 
     if (hdr->reserved[kCtlSkip + pass]) return;
     const bool src_is_alt = hdr->reserved[kCtlSrcIsAlt + pass] != 0;
+    PassContext<K, V, SW> c;
     // Buffer 0 is the caller's (possibly strided) view, buffer 1 the dense alternate.
-    const K *src = src_is_alt ? buf1 : buf0;
-    K *dst = src_is_alt ? buf0 : buf1;
-    const int64_t src_stride = src_is_alt ? 1 : stride0;
-    const int64_t dst_stride = src_is_alt ? stride0 : 1;
-    const V *vsrc = src_is_alt ? val1 : val0;
-    V *vdst = src_is_alt ? val0 : val1;
-
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    unsigned int *warp_cnt = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE);
-    unsigned int *misc = warp_cnt + WARPS * kRadix + 2 * kRadix;
-
-    const int tid = threadIdx.x;
-    if constexpr (Digit::kUsesIndex) {
-        unsigned char *after_digits = reinterpret_cast<unsigned char *>(misc + 16) + TILE;
-        dg.stage(reinterpret_cast<K *>(after_digits + kRadix * 8), reinterpret_cast<int64_t *>(after_digits));
-    }
-    if (tid == 0) misc[0] = atomicAdd(&hdr->reserved[kCtlTicket + pass], 1u);
-    for (int i = tid; i < WARPS * kRadix; i += THREADS) warp_cnt[i] = 0u;
-    __syncthreads();
-    const int tile = (int)misc[0];
-
+    c.src = src_is_alt ? buf1 : buf0;
+    c.dst = src_is_alt ? buf0 : buf1;
+    c.src_stride = src_is_alt ? 1 : stride0;
+    c.dst_stride = src_is_alt ? stride0 : 1;
+    c.vsrc = src_is_alt ? val1 : val0;
+    c.vdst = src_is_alt ? val0 : val1;
+    c.n = n;
+    c.num_tiles = num_tiles;
+    c.dense = stride0 == 1;
+    c.hdr = hdr;
+    c.gbase = gbase_all + pass * kRadix;
     // Two look-back arrays alternate between the passes that run; this pass clears the
     // slots the next one will use (the previous pass, their last user, has completed).
-    SW *status = status_all + (src_is_alt ? (size_t)num_tiles * kRadix : 0);
-    SW *status_next = status_all + (src_is_alt ? 0 : (size_t)num_tiles * kRadix);
-    const unsigned int *gbase = gbase_all + pass * kRadix;
+    c.status = status_all + (src_is_alt ? (size_t)num_tiles * kRadix : 0);
+    c.status_next = status_all + (src_is_alt ? 0 : (size_t)num_tiles * kRadix);
 
-    const bool fast = stride0 == 1 && (int64_t)(tile + 1) * TILE <= n;
-    if (fast)
-        onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, true>(src, 1, dst, 1, vsrc, vdst, n, tile, dg, hdr, gbase, status,
-                                                            status_next, smem_raw);
-    else
-        onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, false>(src, src_stride, dst, dst_stride, vsrc, vdst, n, tile, dg, hdr,
-                                                             gbase, status, status_next, smem_raw);
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    if constexpr (Digit::kUsesIndex) {
+        unsigned char *after_digits =
+            smem_raw + (size_t)TILE * L::STAGE + (size_t)(THREADS / 32) * kRadix * 8 + kRadix * 8 + 64 + TILE;
+        dg.stage(reinterpret_cast<K *>(after_digits + kRadix * 8), reinterpret_cast<int64_t *>(after_digits));
+    }
+
+    int tile = (int)blockIdx.x;
+    if (tile >= num_tiles) return;
+    K key[ITEMS];
+    load_tile_keys<K, V, SW, THREADS, ITEMS>(key, c, tile);
+    while (true) {
+        const int next_tile = tile + (int)gridDim.x;
+        if (c.dense && (int64_t)(tile + 1) * TILE <= n)
+            onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, true>(key, c, tile, next_tile, dg, smem_raw);
+        else
+            onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, false>(key, c, tile, next_tile, dg, smem_raw);
+        if (next_tile >= num_tiles) break;
+        tile = next_tile;
+    }
 }
 
 // ---- 4. bring the result home when it ended in the alternate buffer ---------------------
@@ -508,16 +623,21 @@ static SortLayout sort_layout(int key_bytes, int value_bytes, int64_t n) {
     return L;
 }
 
+// Opts the kernel in to its dynamic shared memory and asks how many of its blocks fit on one
+// SM; once per kernel instantiation, device and host thread.
 template <typename KernelT>
-static int allow_dynamic_smem(KernelT kernel, size_t bytes) {
-    // One cudaFuncSetAttribute per kernel instantiation, device and host thread.
+static int configure_persistent(KernelT kernel, int threads, size_t bytes, int *blocks_per_sm) {
     static thread_local int configured_device = -1;
+    static thread_local int cached_blocks = 0;
     int dev = 0;
     B200ALG_CUDA_TRY(cudaGetDevice(&dev));
     if (configured_device != dev) {
         B200ALG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        B200ALG_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&cached_blocks, kernel, threads, bytes));
+        if (cached_blocks < 1) return B200ALG_UNSUPPORTED;
         configured_device = dev;
     }
+    *blocks_per_sm = cached_blocks;
     return B200ALG_OK;
 }
 
@@ -527,10 +647,13 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
     constexpr int THREADS = SortTuning<K>::THREADS, ITEMS = SortTuning<K>::ITEMS;
     using Smem = OnesweepSmem<K, V, false, THREADS, ITEMS>;
     auto kernel = onesweep_kernel<K, V, SW, RadixDigit<K, XF>, THREADS, ITEMS>;
+    int blocks_per_sm = 0;
     {
-        const int rc = allow_dynamic_smem(kernel, Smem::bytes);
+        const int rc = configure_persistent(kernel, THREADS, Smem::bytes, &blocks_per_sm);
         if (rc != B200ALG_OK) return rc;
     }
+    const int64_t resident = (int64_t)sm_count() * blocks_per_sm;
+    const int grid = (int)(L.tiles < resident ? L.tiles : resident);
     char *t = (char *)temp;
     TempHeader *hdr = (TempHeader *)temp;
     unsigned int *ghist = (unsigned int *)(t + L.off_ghist);
@@ -554,8 +677,8 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
         RadixDigit<K, XF> dg;
         if constexpr (std::is_same<XF, KeyXform<K>>::value) dg.xf = xf;
         dg.shift = p * 8;
-        kernel<<<(int)L.tiles, THREADS, Smem::bytes, s>>>(keys, stride, alt_keys, values, alt_vals, n, p, dg, hdr, gbase,
-                                                          status, (int)L.tiles);
+        kernel<<<grid, THREADS, Smem::bytes, s>>>(keys, stride, alt_keys, values, alt_vals, n, p, dg, hdr, gbase, status,
+                                                  (int)L.tiles);
         B200ALG_LAUNCH_CHECK();
     }
     {
@@ -623,10 +746,13 @@ static int run_partition(cudaStream_t s, const K *keys, const V *values, int64_t
     constexpr int THREADS = SortTuning<K>::THREADS, ITEMS = SortTuning<K>::ITEMS;
     using Smem = OnesweepSmem<K, V, true, THREADS, ITEMS>;
     auto kernel = onesweep_kernel<K, V, SW, SplitterBucket<K>, THREADS, ITEMS>;
+    int blocks_per_sm = 0;
     {
-        const int rc = allow_dynamic_smem(kernel, Smem::bytes);
+        const int rc = configure_persistent(kernel, THREADS, Smem::bytes, &blocks_per_sm);
         if (rc != B200ALG_OK) return rc;
     }
+    const int64_t resident = (int64_t)sm_count() * blocks_per_sm;
+    const int grid = (int)(L.tiles < resident ? L.tiles : resident);
     char *t = (char *)temp;
     TempHeader *hdr = (TempHeader *)temp;
     unsigned int *ghist = (unsigned int *)(t + L.off_ghist);
@@ -646,8 +772,8 @@ static int run_partition(cudaStream_t s, const K *keys, const V *values, int64_t
     B200ALG_LAUNCH_CHECK();
     export_bucket_counts_kernel<<<1, kRadix, 0, s>>>(ghist, counts, num_buckets);
     B200ALG_LAUNCH_CHECK();
-    kernel<<<(int)L.tiles, THREADS, Smem::bytes, s>>>(const_cast<K *>(keys), 1, out_keys, const_cast<V *>(values), out_values,
-                                                      n, 0, dg, hdr, gbase, status, (int)L.tiles);
+    kernel<<<grid, THREADS, Smem::bytes, s>>>(const_cast<K *>(keys), 1, out_keys, const_cast<V *>(values), out_values, n, 0,
+                                              dg, hdr, gbase, status, (int)L.tiles);
     B200ALG_LAUNCH_CHECK();
     return B200ALG_OK;
 }
@@ -774,3 +900,10 @@ extern "C" int b200alg_bucket_partition(void *stream, const void *keys, const vo
     }
     return B200ALG_UNSUPPORTED;
 }
+
+#ifdef B200ALG_EXP_TIMING
+extern "C" int b200alg_exp_set_debug(void *ptr) {
+    B200ALG_CUDA_TRY(cudaMemcpyToSymbol(b200alg::g_exp_debug, &ptr, sizeof(ptr)));
+    return B200ALG_OK;
+}
+#endif
