@@ -48,12 +48,13 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index = index
         self.lines: list[str] = []
+        self.first = 0
         self.proc = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -63,6 +64,10 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def mark(self):
+        """Forget the samples taken so far (warm-up)."""
+        self.first = len(self.lines)
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -70,7 +75,7 @@ class ClockSampler:
         self.proc.terminate()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in self.lines[max(0, self.first - 1):]:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -209,6 +214,54 @@ def secondary_metrics(acc, peak_gbs: float) -> dict:
     return out
 
 
+def run_profile_case(case: str) -> None:
+    """Three launches of one primitive on a case that is larger than L2 but holds at most a
+    few GB on the device: what an `ncu` capture is pointed at."""
+    import torch
+    import ilgpu_b200 as ib
+    from ilgpu_b200 import synthetic
+    acc = ib.Accelerator(0)
+    Ops, Sorts = ib.ScanReduceOperations, ib.RadixSortOperations
+    if case == "sort":
+        n = 1 << 26
+        temp = acc.Allocate1D(acc.ComputeRadixSortTempStorageSize(Sorts.AscendingUInt32, n), torch.int32)
+        sort = acc.CreateRadixSort(Sorts.AscendingUInt32)
+        for r in range(3):
+            keys = synthetic.uniform_uint32_device(n, SEED + r, "cuda")
+            sort(None, keys, temp)
+    elif case == "sort_pairs":
+        n = 1 << 25
+        vals = torch.arange(n, dtype=torch.int32, device="cuda").view(torch.uint32)
+        temp = acc.Allocate1D(acc.ComputeRadixSortPairsTempStorageSize(Sorts.AscendingUInt64, vals.dtype, n), torch.int32)
+        sort = acc.CreateRadixSortPairs(Sorts.AscendingUInt64)
+        for r in range(3):
+            keys = synthetic.zipf_uint64_device(n, 4 + r, "cuda")
+            sort(None, keys, vals.clone(), temp)
+    elif case == "scan":
+        n = 1 << 28
+        x = synthetic.uniform_float32_device(n, 5, "cuda")
+        y = torch.empty_like(x)
+        temp = acc.Allocate1D(acc.ComputeScanTempStorageSize(torch.float32, n), torch.int32)
+        scan = acc.CreateScan(Ops.AddFloat, ib.ScanKind.Inclusive)
+        for _ in range(3):
+            scan(None, x, y, temp)
+    elif case == "reduce":
+        n = 1 << 28
+        x = synthetic.uniform_float32_device(n, 5, "cuda")
+        cell = acc.Allocate1D(1, torch.float32)
+        for _ in range(3):
+            acc.CreateReduction(Ops.AddFloat)(None, x, cell)
+    else:
+        n = 1 << 28
+        f = synthetic.normal_float32_device(n, 3, "cuda")
+        bins = torch.zeros(256, dtype=torch.int32, device="cuda")
+        ovf = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for _ in range(3):
+            acc.Histogram(None, f, bins, ovf, ib.EqualWidthClampLocator(-4.0, 4.0))
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": case, "ok": True}))
+
+
 def run_native(args) -> None:
     import numpy as np
     import torch
@@ -242,7 +295,7 @@ def run_native(args) -> None:
 
         def step_fn(i):
             sort(None, bufs[i], temp)
-        launches_per_step = 7   # histogram, offsets, 4 digit passes, copy-back (exits at once)
+        launches_per_step = 7   # digit histograms, offsets, 4 digit passes, copy-back (exits at once)
         result_of = lambda i: bufs[i]
     else:
         from ilgpu_b200.multi_gpu import ShardedAlgorithms
@@ -255,13 +308,14 @@ def run_native(args) -> None:
         launches_per_step = sharded.sort_launches_per_step(op)
         result_of = lambda i: last[0][0]
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()          # nvidia-smi takes a moment to start: launch it before the warm-up
     for i in range(warmup):
         step_fn(i)
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.mark()           # samples from here on belong to the timed region
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
@@ -367,10 +421,14 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the scan / reduce / histogram figures")
+    ap.add_argument("--profile-case", choices=["sort", "sort_pairs", "scan", "reduce", "histogram"],
+                    help="run a few launches of one primitive on a small case and exit (the target of ncu captures)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_native(args)

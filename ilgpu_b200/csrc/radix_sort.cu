@@ -245,7 +245,7 @@ struct OnesweepSmem {
 #define B200ALG_BALLOT_ITEMS 4
 #endif
 #ifndef B200ALG_LOOK_WINDOW
-#define B200ALG_LOOK_WINDOW 1
+#define B200ALG_LOOK_WINDOW 4
 #endif
 
 #ifdef B200ALG_EXP_TIMING
