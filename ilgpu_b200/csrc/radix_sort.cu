@@ -192,6 +192,11 @@ template <typename K> struct SplitterBucket {
     const int64_t *splitter_index;
     int num_splitters;
     int64_t index_base;
+    // Optional: where each bucket of this shard goes (device arrays of num_splitters + 1
+    // pointers; the targets may be peer-GPU memory mapped into this process).  When set, the
+    // pass stores bucket b's elements at bucket_keys[b][0..count_b) instead of one output array.
+    void *const *bucket_keys;
+    void *const *bucket_values;
     // Copies the splitters into shared memory (keys already transformed) and reads them from
     // there afterwards.  Call with all threads of the block, then synchronise.
     __device__ __forceinline__ void stage(K *shared_keys, int64_t *shared_index) {
@@ -499,7 +504,16 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
             unsigned int d;
             if constexpr (Digit::kUsesIndex) d = sdigit[p]; else d = dg(k, 0);
             out_idx[i] = bin_goff[d] + (unsigned int)p;
-            if (FAST) c.dst[out_idx[i]] = k; else c.dst[(int64_t)out_idx[i] * c.dst_stride] = k;
+            bool stored = false;
+            if constexpr (Digit::kUsesIndex) {
+                if (dg.bucket_keys) {  // plain stores, possibly over NVLink into a peer's receive buffer
+                    reinterpret_cast<K *>(dg.bucket_keys[d])[out_idx[i]] = k;
+                    stored = true;
+                }
+            }
+            if (!stored) {
+                if (FAST) c.dst[out_idx[i]] = k; else c.dst[(int64_t)out_idx[i] * c.dst_stride] = k;
+            }
         }
     }
 
@@ -515,7 +529,16 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
             const int p = tid + i * THREADS;
-            if (FAST || p < valid) c.vdst[out_idx[i]] = svals[p];
+            if (FAST || p < valid) {
+                bool stored = false;
+                if constexpr (Digit::kUsesIndex) {
+                    if (dg.bucket_values) {
+                        reinterpret_cast<V *>(dg.bucket_values[sdigit[p]])[out_idx[i]] = svals[p];
+                        stored = true;
+                    }
+                }
+                if (!stored) c.vdst[out_idx[i]] = svals[p];
+            }
         }
     }
     B200ALG_STAMP(8);
@@ -778,12 +801,110 @@ static int run_partition(cudaStream_t s, const K *keys, const V *values, int64_t
     return B200ALG_OK;
 }
 
+// Bucket sizes only (the first half of a partition whose second half scatters to peers).
+template <typename K>
+static int run_bucket_count(cudaStream_t s, const K *keys, int64_t n, const SplitterBucket<K> &dg, int64_t *counts,
+                            int num_buckets, void *temp, const SortLayout &L) {
+    unsigned int *ghist = (unsigned int *)((char *)temp + L.off_ghist);
+    B200ALG_CUDA_TRY(cudaMemsetAsync(ghist, 0, kRadix * sizeof(unsigned int), s));
+    int64_t want = ceil_div(n, 256 * 8);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    bucket_histogram_kernel<K><<<blocks, 256, 0, s>>>(keys, n, dg, ghist);
+    B200ALG_LAUNCH_CHECK();
+    export_bucket_counts_kernel<<<1, kRadix, 0, s>>>(ghist, counts, num_buckets);
+    B200ALG_LAUNCH_CHECK();
+    return B200ALG_OK;
+}
+
+// The partition pass with one destination per bucket (dg.bucket_keys / dg.bucket_values).
+template <typename K, typename V, typename SW>
+static int run_bucket_scatter(cudaStream_t s, const K *keys, const V *values, int64_t n, const SplitterBucket<K> &dg,
+                              void *temp, const SortLayout &L) {
+    constexpr int THREADS = SortTuning<K>::THREADS, ITEMS = SortTuning<K>::ITEMS;
+    using Smem = OnesweepSmem<K, V, true, THREADS, ITEMS>;
+    auto kernel = onesweep_kernel<K, V, SW, SplitterBucket<K>, THREADS, ITEMS>;
+    int blocks_per_sm = 0;
+    {
+        const int rc = configure_persistent(kernel, THREADS, Smem::bytes, &blocks_per_sm);
+        if (rc != B200ALG_OK) return rc;
+    }
+    const int64_t resident = (int64_t)sm_count() * blocks_per_sm;
+    const int grid = (int)(L.tiles < resident ? L.tiles : resident);
+    char *t = (char *)temp;
+    TempHeader *hdr = (TempHeader *)temp;
+    unsigned int *ghist = (unsigned int *)(t + L.off_ghist);
+    unsigned int *gbase = (unsigned int *)(t + L.off_gbase);
+    SW *status = (SW *)(t + L.off_status);
+    B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)L.control_bytes, s));
+    // all-zero histogram: the bucket offsets come out zero (every bucket has its own base
+    // pointer) and the pass is scheduled from buffer 0
+    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (unsigned int)n + 1u);
+    B200ALG_LAUNCH_CHECK();
+    kernel<<<grid, THREADS, Smem::bytes, s>>>(const_cast<K *>(keys), 1, nullptr, const_cast<V *>(values), nullptr, n, 0, dg, hdr,
+                                              gbase, status, (int)L.tiles);
+    B200ALG_LAUNCH_CHECK();
+    return B200ALG_OK;
+}
+
+template <typename K, typename V>
+static int scatter_typed(cudaStream_t s, const void *keys, const void *values, int64_t n, const SplitterBucket<K> &dg, void *temp,
+                         const SortLayout &L) {
+    if (L.wide_status) return run_bucket_scatter<K, V, unsigned long long>(s, (const K *)keys, (const V *)values, n, dg, temp, L);
+    return run_bucket_scatter<K, V, unsigned int>(s, (const K *)keys, (const V *)values, n, dg, temp, L);
+}
+
+template <typename K>
+static int bucket_ops_for_key(cudaStream_t s, bool scatter, const void *keys, const void *values, int64_t n, int value_bytes,
+                              uint64_t xn, uint64_t xp, const void *sk, const int64_t *si, int ns, int64_t base,
+                              void *const *bucket_keys, void *const *bucket_values, int64_t *counts, void *temp,
+                              const SortLayout &L) {
+    SplitterBucket<K> dg{KeyXform<K>{(K)xn, (K)xp}, (const K *)sk, si, ns, base, bucket_keys, bucket_values};
+    if (!scatter) return run_bucket_count<K>(s, (const K *)keys, n, dg, counts, ns + 1, temp, L);
+    switch (value_bytes) {
+    case 0: return scatter_typed<K, NoValue>(s, keys, values, n, dg, temp, L);
+    case 4: return scatter_typed<K, uint32_t>(s, keys, values, n, dg, temp, L);
+    case 8: return scatter_typed<K, uint64_t>(s, keys, values, n, dg, temp, L);
+    }
+    return B200ALG_UNSUPPORTED;
+}
+
+static int bucket_ops(void *stream, bool scatter, const void *keys, const void *values, int64_t n, int key_dtype, int value_bytes,
+                      int order, const void *splitter_keys, const int64_t *splitter_index, int num_splitters,
+                      int64_t index_base, void *const *bucket_keys, void *const *bucket_values, int64_t *counts, void *temp,
+                      int64_t temp_bytes) {
+    if (!keys || !temp) return B200ALG_INVALID_ARGUMENT;
+    if (n < 0 || num_splitters < 0 || num_splitters > 254) return B200ALG_INVALID_ARGUMENT;
+    if (num_splitters && (!splitter_keys || !splitter_index)) return B200ALG_INVALID_ARGUMENT;
+    const int kb = dtype_bytes(key_dtype);
+    if (kb == 0) return B200ALG_UNSUPPORTED;
+    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (((uintptr_t)keys % kb) || ((uintptr_t)temp % 256)) return B200ALG_MISALIGNED;
+    uint64_t xn, xp;
+    if (!key_xform_constants(key_dtype, order, xn, xp)) return B200ALG_UNSUPPORTED;
+    const SortLayout L = sort_layout(kb, 0, n);
+    if (temp_bytes < L.control_bytes) return B200ALG_TEMP_TOO_SMALL;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n == 0) {
+        if (!scatter) B200ALG_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int64_t) * (num_splitters + 1), s));
+        return B200ALG_OK;
+    }
+    switch (kb) {
+    case 1: return bucket_ops_for_key<uint8_t>(s, scatter, keys, values, n, value_bytes, xn, xp, splitter_keys, splitter_index, num_splitters, index_base, bucket_keys, bucket_values, counts, temp, L);
+    case 2: return bucket_ops_for_key<uint16_t>(s, scatter, keys, values, n, value_bytes, xn, xp, splitter_keys, splitter_index, num_splitters, index_base, bucket_keys, bucket_values, counts, temp, L);
+    case 4: return bucket_ops_for_key<uint32_t>(s, scatter, keys, values, n, value_bytes, xn, xp, splitter_keys, splitter_index, num_splitters, index_base, bucket_keys, bucket_values, counts, temp, L);
+    case 8: return bucket_ops_for_key<uint64_t>(s, scatter, keys, values, n, value_bytes, xn, xp, splitter_keys, splitter_index, num_splitters, index_base, bucket_keys, bucket_values, counts, temp, L);
+    }
+    return B200ALG_UNSUPPORTED;
+}
+
 template <typename K, typename V>
 static int partition_typed(cudaStream_t s, const void *keys, const void *values, int64_t n, uint64_t xn, uint64_t xp,
                            const void *splitter_keys, const int64_t *splitter_index, int num_splitters,
                            int64_t index_base, void *out_keys, void *out_values, int64_t *counts, void *temp,
                            const SortLayout &L) {
-    SplitterBucket<K> dg{KeyXform<K>{(K)xn, (K)xp}, (const K *)splitter_keys, splitter_index, num_splitters, index_base};
+    SplitterBucket<K> dg{KeyXform<K>{(K)xn, (K)xp}, (const K *)splitter_keys, splitter_index, num_splitters, index_base,
+                         nullptr, nullptr};
     if (L.wide_status)
         return run_partition<K, V, unsigned long long>(s, (const K *)keys, (const V *)values, n, dg, (K *)out_keys,
                                                        (V *)out_values, counts, num_splitters + 1, temp, L);
@@ -907,3 +1028,22 @@ extern "C" int b200alg_exp_set_debug(void *ptr) {
     return B200ALG_OK;
 }
 #endif
+
+extern "C" int b200alg_bucket_count(void *stream, const void *keys, int64_t n, int key_dtype, int order,
+                                    const void *splitter_keys, const int64_t *splitter_index, int num_splitters,
+                                    int64_t index_base, int64_t *bucket_counts, void *temp, int64_t temp_bytes) {
+    if (!bucket_counts || ((uintptr_t)bucket_counts % 8)) return B200ALG_INVALID_ARGUMENT;
+    return bucket_ops(stream, false, keys, nullptr, n, key_dtype, 0, order, splitter_keys, splitter_index, num_splitters,
+                      index_base, nullptr, nullptr, bucket_counts, temp, temp_bytes);
+}
+
+extern "C" int b200alg_bucket_scatter(void *stream, const void *keys, const void *values, int64_t n, int key_dtype,
+                                      int value_bytes, int order, const void *splitter_keys, const int64_t *splitter_index,
+                                      int num_splitters, int64_t index_base, void *const *bucket_key_ptrs,
+                                      void *const *bucket_value_ptrs, void *temp, int64_t temp_bytes) {
+    if (!bucket_key_ptrs || (value_bytes && (!values || !bucket_value_ptrs))) return B200ALG_INVALID_ARGUMENT;
+    if (value_bytes != 0 && value_bytes != 4 && value_bytes != 8) return B200ALG_UNSUPPORTED;
+    return bucket_ops(stream, true, keys, values, n, key_dtype, value_bytes, order, splitter_keys, splitter_index,
+                      num_splitters, index_base, bucket_key_ptrs, value_bytes ? bucket_value_ptrs : nullptr, nullptr, temp,
+                      temp_bytes);
+}

@@ -94,6 +94,78 @@ class NativeEngine:
                 _ptr(out_keys), _ptr(out_values), _ptr(counts), _ptr(temp), temp.numel() * 4))
         return out_keys, out_values, counts
 
+    # -- the partition in two steps, with the exchange fused into the second one --
+    supports_peer_scatter = True
+
+    def _partition_temp(self, keys) -> torch.Tensor:
+        need = ctypes.c_int64(0)
+        B200AlgException.ThrowIfFailed(self.acc.L.b200alg_bucket_partition_temp_bytes(
+            dtype_code(keys.dtype), keys.numel(), ctypes.byref(need)))
+        return self._temp("partition", (need.value + 3) // 4)
+
+    def bucket_count(self, keys, op: RadixSortOperation, splitter_keys, splitter_index, index_base: int) -> torch.Tensor:
+        temp = self._partition_temp(keys)
+        counts = self.empty(splitter_keys.numel() + 1, torch.int64)
+        with self.acc.Bind():
+            B200AlgException.ThrowIfFailed(self.acc.L.b200alg_bucket_count(
+                _stream_ptr(None), _ptr(keys), keys.numel(), dtype_code(keys.dtype),
+                N.SORT_DESCENDING if op.descending else 0, _ptr(splitter_keys), _ptr(splitter_index),
+                splitter_keys.numel(), int(index_base), _ptr(counts), _ptr(temp), temp.numel() * 4))
+        return counts
+
+    def bucket_scatter(self, keys, values, op: RadixSortOperation, splitter_keys, splitter_index, index_base: int,
+                       key_pointers: list[int], value_pointers: list[int] | None) -> None:
+        """Stores bucket b of this shard at key_pointers[b] (an address that may lie in a peer
+        GPU's receive buffer): partition and exchange in one kernel."""
+        temp = self._partition_temp(keys)
+        table = torch.tensor(key_pointers + (value_pointers or []), dtype=torch.int64).to(self.device, non_blocking=True)
+        nb = len(key_pointers)
+        vtable = table[nb:] if value_pointers else None
+        with self.acc.Bind():
+            B200AlgException.ThrowIfFailed(self.acc.L.b200alg_bucket_scatter(
+                _stream_ptr(None), _ptr(keys), _ptr(values), keys.numel(), dtype_code(keys.dtype),
+                0 if values is None else values.dtype.itemsize, N.SORT_DESCENDING if op.descending else 0,
+                _ptr(splitter_keys), _ptr(splitter_index), splitter_keys.numel(), int(index_base),
+                _ptr(table), _ptr(vtable), _ptr(temp), temp.numel() * 4))
+        self._keepalive = table   # the kernel reads the table asynchronously
+
+    def peer_buffers(self, group, capacity: int) -> "PeerBuffers":
+        pb = getattr(self, "_peer_buffers", None)
+        if pb is None or pb.capacity < capacity:
+            pb = PeerBuffers(group, self.device, max(capacity, 1 << 16))
+            self._peer_buffers = pb
+        return pb
+
+
+class PeerBuffers:
+    """Receive buffers that every rank of the group can store into: one symmetric-memory
+    allocation per rank, mapped into all processes of the node (NVLink peer access).  The
+    first half takes keys, the second half values; `capacity` is in elements of 8 bytes."""
+
+    def __init__(self, group, device, capacity: int):
+        import torch.distributed._symmetric_memory as symm
+        self.capacity = int(capacity)
+        self.buffer = symm.empty(self.capacity * 16, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.buffer, group)
+        self.pointers = [int(p) for p in self.handle.buffer_ptrs]
+
+    def key_pointer(self, rank: int) -> int:
+        return self.pointers[rank]
+
+    def value_pointer(self, rank: int) -> int:
+        return self.pointers[rank] + self.capacity * 8
+
+    def local_keys(self, count: int, dtype: torch.dtype) -> torch.Tensor:
+        return self.buffer[: count * dtype.itemsize].view(dtype)
+
+    def local_values(self, count: int, dtype: torch.dtype) -> torch.Tensor:
+        start = self.capacity * 8
+        return self.buffer[start: start + count * dtype.itemsize].view(dtype)
+
+    def barrier(self, channel: int) -> None:
+        """Device-side barrier over the group, enqueued on the current stream."""
+        self.handle.barrier(channel=channel)
+
 
 def _identity_tensor(op: ScanReduceOperation, device) -> torch.Tensor:
     """One element holding the operation's Identity (0, MinValue or MaxValue)."""
@@ -133,6 +205,7 @@ class ShardedAlgorithms:
     """The primitives over all ranks of a process group (one rank per GPU)."""
 
     SAMPLES_PER_RANK = 2048
+    use_peer_scatter = True   # False: exchange the buckets with an NCCL all-to-all instead
 
     def __init__(self, engine, group=None):
         self.engine = NativeEngine(engine) if isinstance(engine, Accelerator) else engine
@@ -241,6 +314,9 @@ class ShardedAlgorithms:
         splitter_keys = _signed_view(all_keys)[cut].view(keys.dtype).contiguous()
         splitter_index = all_index[cut].contiguous()
 
+        if G > 1 and getattr(eng, "supports_peer_scatter", False) and self.use_peer_scatter:
+            return self._exchange_by_peer_stores(keys, values, operation, splitter_keys, splitter_index, base)
+
         # 2. stable partition of the shard into one bucket per rank
         if n:
             out_keys, out_values, counts = eng.partition(keys, values, operation, splitter_keys, splitter_index, base)
@@ -260,6 +336,39 @@ class ShardedAlgorithms:
 
         # 4. received runs lie in source-rank order; a stable local sort finishes the job
         if recv_keys.numel():
+            eng.sort(recv_keys, recv_values, operation)
+        return recv_keys, recv_values
+
+    def _exchange_by_peer_stores(self, keys, values, operation, splitter_keys, splitter_index, base):
+        """Steps 2-4 with the exchange fused into the partition: the partition kernel stores
+        every bucket straight into its owner's receive buffer (peer memory over NVLink), so
+        the data is written once and no separate all-to-all runs."""
+        eng, G, r = self.engine, self.world, self.rank
+        n = keys.numel()
+        device = keys.device
+        if n:
+            counts = eng.bucket_count(keys, operation, splitter_keys, splitter_index, base)
+        else:
+            counts = torch.zeros(G, dtype=torch.int64, device=device)
+        matrix = self._all_gather(counts).view(G, G).tolist()      # matrix[src][dst]; the one host sync
+        column = [sum(matrix[src][dst] for src in range(G)) for dst in range(G)]
+        peers = eng.peer_buffers(self.group, 2 * max(column))      # same decision on every rank
+        kb = keys.dtype.itemsize
+        # my block inside rank b's buffer starts after the blocks of the lower ranks
+        start = [sum(matrix[src][b] for src in range(r)) for b in range(G)]
+        key_pointers = [peers.key_pointer(b) + start[b] * kb for b in range(G)]
+        value_pointers = None
+        if values is not None:
+            vb = values.dtype.itemsize
+            value_pointers = [peers.value_pointer(b) + start[b] * vb for b in range(G)]
+        peers.barrier(channel=0)      # every rank is done with what the previous call left in its buffer
+        if n:
+            eng.bucket_scatter(keys, values, operation, splitter_keys, splitter_index, base, key_pointers, value_pointers)
+        peers.barrier(channel=1)      # every rank's stores have landed
+        total = column[r]
+        recv_keys = peers.local_keys(total, keys.dtype).clone()
+        recv_values = None if values is None else peers.local_values(total, values.dtype).clone()
+        if total:
             eng.sort(recv_keys, recv_values, operation)
         return recv_keys, recv_values
 

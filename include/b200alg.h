@@ -105,6 +105,21 @@ int b200alg_bucket_partition(void *stream, const void *keys, const void *values,
                              void *out_keys, void *out_values, int64_t *bucket_counts, void *temp,
                              int64_t temp_bytes);
 
+/* The same partition in two steps, for a sort whose exchange is fused into the partition:
+ * b200alg_bucket_count only sizes the buckets; after the ranks have exchanged the sizes,
+ * b200alg_bucket_scatter stores bucket b of this shard at bucket_key_ptrs[b][0..count_b)
+ * (and bucket_value_ptrs[b][...]), in input order.  The pointer tables are device arrays
+ * of num_splitters + 1 entries; an entry may point into another GPU's memory that is
+ * mapped into this process (the stores then travel over NVLink; plain stores, no TMA). */
+int b200alg_bucket_count(void *stream, const void *keys, int64_t n, int key_dtype, int order,
+                         const void *splitter_keys, const int64_t *splitter_index, int num_splitters,
+                         int64_t index_base, int64_t *bucket_counts, void *temp, int64_t temp_bytes);
+int b200alg_bucket_scatter(void *stream, const void *keys, const void *values, int64_t n, int key_dtype,
+                           int value_bytes, int order, const void *splitter_keys,
+                           const int64_t *splitter_index, int num_splitters, int64_t index_base,
+                           void *const *bucket_key_ptrs, void *const *bucket_value_ptrs, void *temp,
+                           int64_t temp_bytes);
+
 /* ---- scan -------------------------------------------------------------------------
  * Replaces the lambda of CreateScan (ScanExtensions.cs:930-959 -> SinglePassScanKernel
  * :530-706).  out[i*out_stride] = fold(op, in[0..i]) (inclusive) or fold(op, in[0..i-1])
