@@ -29,6 +29,9 @@ sys.path.insert(0, ROOT)
 KEYS_PER_GPU = 1 << 26
 SORT_BYTES_PER_KEY = 36          # 4-byte keys: one histogram read + 4 x (read + write)
 SEED = 2
+# dram__bytes_read.sum + dram__bytes_write.sum of one sort call of this workload, from the ncu
+# captures summarised under profiles/: histogram pass 268.7 MB + 4 digit passes x 504.4 MB
+SORT_DRAM_TRAFFIC_BYTES = 268.7e6 + 4 * 504.4e6
 
 
 def measured_peaks():
@@ -211,6 +214,67 @@ def secondary_metrics(acc, peak_gbs: float) -> dict:
     for _ in range(3):
         hist(None, f, bins, ovf)
     out["histogram_f32_256bins_2^28"] = gbs(4 * n, time_region(lambda i: hist(None, f, bins, ovf), 5, stream))
+    del f
+    # stable RadixSortPairs of 2^28 uint64 Zipf(1.1) keys with uint32 payload = index; 104 B/pair
+    # (8 + 4 x (16 + 8): the upper four key bytes are constant, so four of eight digit passes run)
+    n = 1 << 28
+    keys0 = synthetic.zipf_uint64_device(n, 4, "cuda")
+    vals0 = torch.arange(n, dtype=torch.int32, device="cuda").view(torch.uint32)
+    op = ib.RadixSortOperations.AscendingUInt64
+    temp = acc.Allocate1D(acc.ComputeRadixSortPairsTempStorageSize(op, torch.uint32, n), torch.int32)
+    sort = acc.CreateRadixSortPairs(op)
+    times = []
+    for r in range(4):
+        k, v = keys0.clone(), vals0.clone()
+        ms = time_region(lambda i: sort(None, k, v, temp), 1, stream)
+        if r:
+            times.append(ms)
+    ms = sum(times) / len(times)
+    out["sort_pairs_u64_u32_zipf_2^28"] = dict(gbs(104 * n, ms), **{"Gpairs/s": round(n / ms / 1e6, 2)})
+    return out
+
+
+def secondary_metrics_sharded(acc, sharded, world: int, rank: int, peak_gbs: float) -> dict:
+    """Scan / reduce / histogram over all GPUs (configs 3 and 5: the totals stay 2^28 and 2^30
+    elements, sharded contiguously), timed on the device, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    import ilgpu_b200 as ib
+    from ilgpu_b200 import synthetic
+    stream = torch.cuda.current_stream()
+    Ops = ib.ScanReduceOperations
+    out = {}
+
+    def agg(nbytes_total, ms):
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        v = nbytes_total / (ms * 1e-3) / 1e9
+        return {"GB/s": round(v, 1), "frac_of_measured_hbm_x_gpus": round(v / (peak_gbs * world), 4), "ms": round(ms, 4)}
+
+    n_total = 1 << 30
+    n = n_total // world
+    x = synthetic.uniform_float32_device(n, 5, "cuda", start=rank * n)
+    y = torch.empty_like(x)
+    for _ in range(3):
+        sharded.Scan(x, y, Ops.AddFloat, ib.ScanKind.Inclusive)
+    dist.barrier()
+    out["scan_f32_inclusive_2^30_total"] = agg(8 * n_total, time_region(lambda i: sharded.Scan(x, y, Ops.AddFloat, ib.ScanKind.Inclusive), 5, stream))
+    for _ in range(3):
+        sharded.Reduce(x, Ops.AddFloat)
+    dist.barrier()
+    out["reduce_f32_sum_2^30_total"] = agg(4 * n_total, time_region(lambda i: sharded.Reduce(x, Ops.AddFloat), 5, stream))
+    del x, y
+    n_total = 1 << 28
+    n = n_total // world
+    f = synthetic.normal_float32_device(n, 3, "cuda", start=rank * n)
+    bins = torch.zeros(256, dtype=torch.int32, device="cuda")
+    ovf = torch.zeros(1, dtype=torch.int32, device="cuda")
+    loc = ib.EqualWidthClampLocator(-4.0, 4.0)
+    for _ in range(3):
+        sharded.Histogram(f, bins, ovf, loc)
+    dist.barrier()
+    out["histogram_f32_256bins_2^28_total"] = agg(4 * n_total, time_region(lambda i: sharded.Histogram(f, bins, ovf, loc), 5, stream))
     return out
 
 
@@ -334,12 +398,12 @@ def run_native(args) -> None:
     value = world * n / (ms_per_step * 1e-3) / 1e9
 
     # sanity of the timed work (the parity tests proper live in tests/)
-    last = result_of(warmup + steps - 1)
-    li = last.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    final = result_of(warmup + steps - 1)
+    li = final.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
     assert bool((li[1:] >= li[:-1]).all()), "result is not sorted"
     if world == 1:
-        assert int(last.view(torch.int32).to(torch.int64).sum().item()) == checksum_in, "keys were lost"
-    del li
+        assert int(final.view(torch.int32).to(torch.int64).sum().item()) == checksum_in, "keys were lost"
+    del li, final
 
     # end to end through the public API with host buffers: H2D of the keys, sort, D2H of the result
     e2e_steps = max(1, min(steps, 8))
@@ -368,6 +432,12 @@ def run_native(args) -> None:
         e2e_ms = float(t.item())
     e2e_value = world * n / (e2e_ms * 1e-3) / 1e9
 
+    secondary = None
+    if world > 1 and not args.no_secondary:
+        del bufs
+        last[0] = None
+        torch.cuda.empty_cache()
+        secondary = secondary_metrics_sharded(acc, sharded, world, rank, peak_gbs)
     if rank != 0:
         if dist is not None:
             dist.barrier()
@@ -387,7 +457,8 @@ def run_native(args) -> None:
         },
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
-            "traffic": None, "peak_kind": peak_kind,
+            "traffic": SORT_DRAM_TRAFFIC_BYTES if world == 1 else None, "traffic_unit": "bytes per sort call (ncu, profiles/)",
+            "peak_kind": peak_kind,
             "kernel": "whole sort call (digit histograms + 4 onesweep passes); 36 B/key algorithmic",
         },
         "e2e": {"value": e2e_value, "unit": "Gkeys/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4 * n,
@@ -395,6 +466,8 @@ def run_native(args) -> None:
         "gpu_launches": launches_per_step * steps,
         "clocks": clocks,
     }
+    if secondary is not None:
+        line["secondary"] = secondary
     if world == 1:
         if not args.no_secondary:
             del bufs

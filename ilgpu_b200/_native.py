@@ -44,6 +44,8 @@ SIGNATURES = {
     "b200alg_histogram": (_int, [_vp, _vp, _i64, _i64, _int, _int, _dbl, _dbl, _vp, _i64, _int, _vp]),
     "b200alg_initialize": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "b200alg_sequence": (_int, [_vp, _vp, _i64, _int, _i64, _i64]),
+    "b200alg_unique_temp_bytes": (_int, [_int, _i64, ctypes.POINTER(_i64)]),
+    "b200alg_unique": (_int, [_vp, _vp, _i64, _int, _vp, _vp, _i64]),
     "b200alg_device_status": (_int, [_vp, _vp]),
 }
 

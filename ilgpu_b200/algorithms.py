@@ -436,6 +436,45 @@ class Accelerator:
         """HistogramLaunchers.tt:71-87."""
         self.CreateHistogram(locator, checked=False)(stream, view, histogram)
 
+    # -- unique (the step after a sort) --
+    def ComputeUniqueTempStorageSize(self, dtype: torch.dtype, dataLength: int) -> int:
+        """UniqueExtensions.cs:114-121; here the temp holds the survivors, so it grows with n."""
+        out = ctypes.c_int64(0)
+        B200AlgException.ThrowIfFailed(self.L.b200alg_unique_temp_bytes(dtype_code(dtype), int(dataLength), ctypes.byref(out)))
+        return _ints(out.value)
+
+    def CreateUnique(self, dtype: torch.dtype):
+        """Returns ``unique(stream, input, output, temp)`` (Unique<T> delegate, UniqueExtensions.cs:25-30):
+        removes consecutive duplicates in place; ``output[0]`` (int64) receives the new length."""
+        code = dtype_code(dtype)
+
+        def unique(stream, input, output, temp):
+            # UniqueExtensions.cs:150-172
+            _check_view(input, "input", dtype)
+            _check_view(output, "output", torch.int64)
+            if temp is None:
+                raise ArgumentNullException("temp")
+            if output.numel() < 1:
+                raise ArgumentOutOfRangeException("output")
+            if _stride(input) != 1:
+                raise NotSupportedException("dense view expected")
+            _check_temp(temp, self.ComputeUniqueTempStorageSize(dtype, input.numel()))
+            if input.numel() > 2**31 - 1:
+                raise NotSupportedException("NotSupportedArrayView64")
+            with self.Bind():
+                B200AlgException.ThrowIfFailed(self.L.b200alg_unique(
+                    _stream_ptr(stream), _ptr(input), input.numel(), code, _ptr(output), _ptr(temp), temp.numel() * 4))
+
+        return unique
+
+    def Unique(self, stream, input: torch.Tensor) -> int:
+        """Allocates output and temp, runs, copies the count back - which synchronises
+        (UniqueExtensions.cs:200-220)."""
+        output = self.Allocate1D(1, torch.int64)
+        temp = self.Allocate1D(self.ComputeUniqueTempStorageSize(input.dtype, input.numel()), torch.int32)
+        self.CreateUnique(input.dtype)(stream, input, output, temp)
+        return int(output.cpu()[0])
+
     # -- edges of the path --
     def Initialize(self, stream, view: torch.Tensor, value) -> None:
         """InitializeExtensions.cs: fills the view with one value."""

@@ -1,5 +1,6 @@
-// Histogram: per-block privatised bins in shared memory (one replica per warp where they
-// fit), flushed with one global atomic per non-empty bin.
+// Histogram: per-block privatised bins in shared memory, replicated per lane so that the
+// shared-memory atomics of a warp fall into distinct banks, flushed with one global atomic
+// per non-empty bin.
 // Replaces HistogramWorkKernel (HistogramExtensions.cs:237-277), which issues one global
 // atomic per element, and the overflow reporting of HistogramKernel (:176-198) with
 // HistogramIncrement* (HistogramOperations.tt:30-41).
@@ -111,12 +112,16 @@ template <typename T, int LOCATOR, bool VECTOR>
 __global__ void __launch_bounds__(kHistThreads)
 histogram_smem_kernel(const T *__restrict__ in, int64_t stride, int64_t n, LocParams p, void *bins, int bin_dtype,
                       int *overflow, int replicas) {
-    extern __shared__ unsigned int sh[];  // replicas x num_bins
+    // Bin b has `replicas` (a power of two, up to 32) counters at sh[b * replicas + r]; lane l
+    // uses r = l % replicas.  With 32 replicas every lane of a warp has a bank of its own, so
+    // an atomic instruction is one wavefront whatever the distribution of the data.
+    extern __shared__ unsigned int sh[];
     const int nb = (int)p.num_bins;
     for (int i = threadIdx.x; i < nb * replicas; i += kHistThreads) sh[i] = 0u;
     __syncthreads();
 
-    unsigned int *mine = sh + ((threadIdx.x >> 5) % replicas) * nb;
+    unsigned int *mine = sh + (threadIdx.x & (replicas - 1));
+    const int rshift = 31 - __clz(replicas);
     const int64_t step = (int64_t)gridDim.x * kHistThreads;
     const int64_t gtid = (int64_t)blockIdx.x * kHistThreads + threadIdx.x;
 
@@ -136,12 +141,12 @@ histogram_smem_kernel(const T *__restrict__ in, int64_t stride, int64_t n, LocPa
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
                 const long long ba = Locate<T, LOCATOR>::run(a.t[k], p);
-                if ((unsigned long long)ba < (unsigned long long)nb) atomicAdd(mine + ba, 1u);
+                if ((unsigned long long)ba < (unsigned long long)nb) atomicAdd(mine + (ba << rshift), 1u);
             }
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
                 const long long bb = Locate<T, LOCATOR>::run(b.t[k], p);
-                if ((unsigned long long)bb < (unsigned long long)nb) atomicAdd(mine + bb, 1u);
+                if ((unsigned long long)bb < (unsigned long long)nb) atomicAdd(mine + (bb << rshift), 1u);
             }
         }
         for (; i < nvec; i += step) {
@@ -150,23 +155,23 @@ histogram_smem_kernel(const T *__restrict__ in, int64_t stride, int64_t n, LocPa
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
                 const long long ba = Locate<T, LOCATOR>::run(a.t[k], p);
-                if ((unsigned long long)ba < (unsigned long long)nb) atomicAdd(mine + ba, 1u);
+                if ((unsigned long long)ba < (unsigned long long)nb) atomicAdd(mine + (ba << rshift), 1u);
             }
         }
         if (blockIdx.x == 0) {
             for (int64_t j = threadIdx.x; j < head; j += kHistThreads) {
                 const long long b = Locate<T, LOCATOR>::run(in[j], p);
-                if ((unsigned long long)b < (unsigned long long)nb) atomicAdd(mine + b, 1u);
+                if ((unsigned long long)b < (unsigned long long)nb) atomicAdd(mine + (b << rshift), 1u);
             }
             for (int64_t j = tail + threadIdx.x; j < n; j += kHistThreads) {
                 const long long b = Locate<T, LOCATOR>::run(in[j], p);
-                if ((unsigned long long)b < (unsigned long long)nb) atomicAdd(mine + b, 1u);
+                if ((unsigned long long)b < (unsigned long long)nb) atomicAdd(mine + (b << rshift), 1u);
             }
         }
     } else {
         for (int64_t i = gtid; i < n; i += step) {
             const long long b = Locate<T, LOCATOR>::run(in[i * stride], p);
-            if ((unsigned long long)b < (unsigned long long)nb) atomicAdd(mine + b, 1u);
+            if ((unsigned long long)b < (unsigned long long)nb) atomicAdd(mine + (b << rshift), 1u);
         }
     }
     __syncthreads();
@@ -174,7 +179,7 @@ histogram_smem_kernel(const T *__restrict__ in, int64_t stride, int64_t n, LocPa
     bool of = false;
     for (int b = threadIdx.x; b < nb; b += kHistThreads) {
         unsigned long long c = 0;
-        for (int r = 0; r < replicas; ++r) c += sh[r * nb + b];
+        for (int r = 0; r < replicas; ++r) c += sh[b * replicas + ((r + threadIdx.x) & (replicas - 1))];
         if (c) of |= add_to_bin(bins, b, c, bin_dtype);
     }
     if (overflow && __syncthreads_or(of) && threadIdx.x == 0) atomicOr(overflow, 1);
@@ -199,8 +204,8 @@ static int launch_histogram(cudaStream_t s, const void *in, int64_t stride, int6
                             int bin_dtype, void *overflow) {
     const int64_t nb = p.num_bins;
     if (nb * 4 <= kHistSmemBytes) {
-        int replicas = (int)(kHistSmemBytes / (nb * 4));
-        if (replicas > kHistWarps) replicas = kHistWarps;
+        int replicas = 1;
+        while (replicas < 32 && (int64_t)replicas * 2 * nb * 4 <= kHistSmemBytes) replicas *= 2;
         const size_t smem = (size_t)replicas * nb * 4;
         constexpr int VEC = 16 / sizeof(T);
         const int64_t per_block = (int64_t)kHistThreads * (stride == 1 ? VEC * 2 : 2);

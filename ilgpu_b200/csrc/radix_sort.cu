@@ -67,22 +67,25 @@ static bool key_xform_constants(int dtype, int order, uint64_t &xn, uint64_t &xp
 
 // ---- 1. histograms of all digit positions ----------------------------------------------
 constexpr int kHistoThreads = 512;
-constexpr int kHistoReplicas = 4;
+constexpr int kHistoReplicas = 8;  // counters per (digit position, digit): lane l uses replica l % 8
 
 template <typename K>
 __global__ void __launch_bounds__(kHistoThreads)
 sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, KeyXform<K> xf, unsigned int *ghist) {
     constexpr int P = sizeof(K);
-    __shared__ unsigned int sh[kHistoReplicas][P][kRadix];
-    for (int i = threadIdx.x; i < kHistoReplicas * P * kRadix; i += kHistoThreads) (&sh[0][0][0])[i] = 0u;
+    // replicas are interleaved ([position][digit][replica]) so that the lanes of a warp spread
+    // over the banks even when their digits collide
+    extern __shared__ unsigned int sh[];  // P x 256 x kHistoReplicas
+    for (int i = threadIdx.x; i < kHistoReplicas * P * kRadix; i += kHistoThreads) sh[i] = 0u;
     __syncthreads();
-    unsigned int(*mine)[kRadix] = sh[(threadIdx.x >> 5) % kHistoReplicas];
+    unsigned int *mine = sh + (threadIdx.x & (kHistoReplicas - 1));
     const int64_t step = (int64_t)gridDim.x * kHistoThreads;
     const int64_t gtid = (int64_t)blockIdx.x * kHistoThreads + threadIdx.x;
     auto count = [&](K raw) {
         const K b = xf(raw);
 #pragma unroll
-        for (int p = 0; p < P; ++p) atomicAdd(&mine[p][(unsigned)(b >> (8 * p)) & 0xFFu], 1u);
+        for (int p = 0; p < P; ++p)
+            atomicAdd(mine + ((p * kRadix + ((unsigned)(b >> (8 * p)) & 0xFFu)) * kHistoReplicas), 1u);
     };
     if (stride == 1) {
         constexpr int VEC = 16 / sizeof(K);
@@ -119,7 +122,7 @@ sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, Key
     for (int i = threadIdx.x; i < P * kRadix; i += kHistoThreads) {
         unsigned int c = 0;
 #pragma unroll
-        for (int r = 0; r < kHistoReplicas; ++r) c += (&sh[r][0][0])[i];
+        for (int r = 0; r < kHistoReplicas; ++r) c += sh[i * kHistoReplicas + ((r + threadIdx.x) & (kHistoReplicas - 1))];
         if (c) atomicAdd(ghist + i, c);
     }
 }
@@ -691,7 +694,17 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
         int64_t want = ceil_div(n, per_block);
         const int64_t cap = (int64_t)sm_count() * (2048 / kHistoThreads);
         const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-        sort_histogram_kernel<K><<<blocks, kHistoThreads, 0, s>>>(keys, stride, n, xf, ghist);
+        constexpr size_t histo_smem = sizeof(K) * kRadix * kHistoReplicas * sizeof(unsigned int);
+        if (histo_smem > 48 * 1024) {
+            static thread_local int histo_device = -1;
+            int dev = 0;
+            B200ALG_CUDA_TRY(cudaGetDevice(&dev));
+            if (histo_device != dev) {
+                B200ALG_CUDA_TRY(cudaFuncSetAttribute(sort_histogram_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)histo_smem));
+                histo_device = dev;
+            }
+        }
+        sort_histogram_kernel<K><<<blocks, kHistoThreads, histo_smem, s>>>(keys, stride, n, xf, ghist);
         B200ALG_LAUNCH_CHECK();
     }
     sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, L.passes, (unsigned int)n);

@@ -172,6 +172,15 @@ int b200alg_initialize(void *stream, void *view, int64_t stride, int64_t n, int 
  * view[i] = (T)(start + i * step); dtype in {I32, U32, I64, U64}. */
 int b200alg_sequence(void *stream, void *view, int64_t n, int dtype, int64_t start, int64_t step);
 
+/* UniqueExtensions.cs:59-195 (CreateUnique with the Comparison{T} operations of
+ * ComparisonOperations.tt): removes consecutive duplicates of data[0..n) in place and stores
+ * the number of elements left in out_count[0] (int64, device).  Integers compare by value;
+ * floating-point values are equal when numerically equal or both NaN (CompareTo).  temp
+ * holds the survivors before they are copied back, so it grows with n (the reference's
+ * ComputeUniqueTempStorageSize is one int because its kernel is a serial chain of groups). */
+int b200alg_unique_temp_bytes(int dtype, int64_t n, int64_t *out_bytes);
+int b200alg_unique(void *stream, void *data, int64_t n, int dtype, void *out_count, void *temp, int64_t temp_bytes);
+
 /* Device-side waits (decoupled look-back) are bounded; when one runs out the kernel
  * records it in `temp` and finishes.  This call copies that record back and
  * SYNCHRONISES `stream`: returns B200ALG_OK or B200ALG_WAIT_LIMIT. */

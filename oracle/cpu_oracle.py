@@ -57,6 +57,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_reduce.argtypes = [i32, i32, vp, i64, i64, vp, i32, i32, i32]
         L.oracle_locate_bin.restype = i64
         L.oracle_locate_bin.argtypes = [i32, u64, i32, dbl, dbl, i64]
+        L.oracle_unique.restype = i64
+        L.oracle_unique.argtypes = [i32, vp, i64]
         L.oracle_histogram.argtypes = [i32, vp, i64, i64, i32, dbl, dbl, i32, vp, i64, vp]
         _lib = L
     return _lib
@@ -149,3 +151,11 @@ def histogram(values: np.ndarray, bins: np.ndarray, locator: str = "equal_width_
                                 bin_code, _ptr(bins), bins.size, _ptr(overflow))
     assert rc == 0, rc
     return bins, overflow
+
+
+def unique(values: np.ndarray) -> np.ndarray:
+    """Consecutive duplicates removed (a copy, cut to the new length)."""
+    _, code = _code(values.dtype)
+    a = np.ascontiguousarray(values).copy()
+    m = lib().oracle_unique(code, _ptr(a), a.size)
+    return a[:m]

@@ -434,6 +434,47 @@ int oracle_histogram(int in_dt, const void *in, int64_t stride, int64_t n, int l
 }
 
 /* ------------------------------------------------------------------------------------
+ * Unique: UniqueKernel (UniqueExtensions.cs:59-112): element i survives when it is the first
+ * one or Compare(input[i], input[i-1]) != 0 with Comparison{T} = first.CompareTo(second)
+ * (ComparisonOperations.tt); survivors are moved to the front in order.  Returns the count.
+ * ---------------------------------------------------------------------------------- */
+static int same_value(int dt, uint64_t a, uint64_t b) {
+    if (dt == DT_F32) {
+        float x, y; uint32_t ua = (uint32_t)a, ub = (uint32_t)b;
+        memcpy(&x, &ua, 4); memcpy(&y, &ub, 4);
+        return x == y || (x != x && y != y);
+    }
+    if (dt == DT_F64) {
+        double x, y;
+        memcpy(&x, &a, 8); memcpy(&y, &b, 8);
+        return x == y || (x != x && y != y);
+    }
+    if (dt == DT_F16) {   /* equal bits, or +0 / -0, or both NaN */
+        uint16_t x = (uint16_t)a, y = (uint16_t)b;
+        int nan_x = (x & 0x7C00) == 0x7C00 && (x & 0x03FF), nan_y = (y & 0x7C00) == 0x7C00 && (y & 0x03FF);
+        if (nan_x || nan_y) return nan_x && nan_y;
+        return x == y || ((x | y) & 0x7FFF) == 0;
+    }
+    return a == b;
+}
+
+int64_t oracle_unique(int dt, void *data, int64_t n) {
+    const int es = dtype_size(dt);
+    uint8_t *d = (uint8_t *)data;
+    int64_t out = 0;
+    uint64_t prev = 0;
+    for (int64_t i = 0; i < n; ++i) {
+        uint64_t cur = load_raw(dt, d, i);
+        if (i == 0 || !same_value(dt, cur, prev)) {
+            memmove(d + out * es, d + i * es, es);
+            ++out;
+        }
+        prev = cur;
+    }
+    return out;
+}
+
+/* ------------------------------------------------------------------------------------
  * Multi-core variant used only as a timed CPU baseline: the same literal two-kernel
  * radix sort, with the (independent) groups of each kernel spread over POSIX threads,
  * which is what a CPUDevice with numMultiprocessors = cores does

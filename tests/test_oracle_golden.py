@@ -148,3 +148,18 @@ def test_equal_width_locator_edges():
     assert loc(3.99) == 255 and loc(4.0) == 255 and loc(1e30) == 255 and loc(-1e30) == 0
     assert loc(float("nan")) == 0 and loc(float("inf")) == 255 and loc(float("-inf")) == 0
     assert loc(0.0) == 128 and loc(-0.0) == 128
+
+
+def test_unique_reference_cases():
+    # UniqueExtensionTests.tt:36-72: the expectation there drops an element equal to the last kept one
+    for tname, t in NP.items():
+        for repeat in (1, 317, 1025):
+            length = 1025 if np.dtype(t).itemsize > 1 else 100
+            host = np.repeat(np.arange(1, length + 1), repeat)[:length].astype(t)
+            kept = [host[0]]
+            for v in host[1:]:
+                if kept[-1] != v:
+                    kept.append(v)
+            np.testing.assert_array_equal(oracle.unique(host), np.asarray(kept, dtype=t))
+    f = np.asarray([0.0, -0.0, np.nan, np.nan, 1.0], dtype=np.float32)   # CompareTo: -0 == 0, NaN == NaN
+    assert oracle.unique(f).size == 3
