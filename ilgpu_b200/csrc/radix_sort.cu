@@ -244,7 +244,10 @@ template <typename K, typename V, bool KEEP_DIGITS, int THREADS, int ITEMS>
 struct OnesweepSmem {
     static constexpr int TILE = THREADS * ITEMS;
     static constexpr int VB = ValueBytes<V>::value;
-    static constexpr int STAGE = (int)sizeof(K) > VB ? (int)sizeof(K) : VB;
+    // keys and values are staged side by side when that stays small enough for two blocks per
+    // SM; otherwise the values reuse the keys' staging buffer in a second round
+    static constexpr bool SPLIT = VB != 0 && (size_t)TILE * ((int)sizeof(K) + VB) <= 72 * 1024;
+    static constexpr int STAGE = SPLIT ? (int)sizeof(K) + VB : ((int)sizeof(K) > VB ? (int)sizeof(K) : VB);
     static constexpr size_t bytes = (size_t)TILE * STAGE + (size_t)(THREADS / 32) * kRadix * 8 + kRadix * 4 * 2 + 64 +
                                     (KEEP_DIGITS ? (size_t)TILE + kRadix * 16 : 0);
 };
@@ -356,6 +359,16 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
     //  - table:   every lane ORs its bit into the digit's mask in the warp's table and reads
     //             the mask back after a warp barrier.
     // After the loop the x fields of the warp's table hold its digit counts.
+    V val[HAS_VALUES ? ITEMS : 1];
+    if constexpr (HAS_VALUES) {  // requested now, needed after the ranking
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int local = warp_base + i * 32;
+            if (FAST || local < valid) val[i] = c.vsrc[tile_base + local];
+        }
+    }
+    V *svals = reinterpret_cast<V *>(smem_raw + (L::SPLIT ? (size_t)TILE * sizeof(K) : 0));
+
     uint2 *my_tbl = warp_tbl + warp * kRadix;
     const unsigned int lt = lanemask_lt();
     const unsigned int my_bit = 1u << lane;
@@ -438,18 +451,11 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
         pos[i] = (packed[i] >> 8) + my_tbl[d].x;
         skeys[pos[i]] = key[i];
         if constexpr (Digit::kUsesIndex) sdigit[pos[i]] = (unsigned char)d;
+        if constexpr (L::SPLIT) svals[pos[i]] = val[i];
     }
 
     // The registers are free again: request the next tile's keys now.
     if (next_tile < c.num_tiles) load_tile_keys<K, V, SW, THREADS, ITEMS>(key, c, next_tile);
-    V val[HAS_VALUES ? ITEMS : 1];
-    if constexpr (HAS_VALUES) {
-#pragma unroll
-        for (int i = 0; i < ITEMS; ++i) {
-            const int local = warp_base + i * 32;
-            if (FAST || local < valid) val[i] = c.vsrc[tile_base + local];
-        }
-    }
     B200ALG_STAMP(5);
 
     // Decoupled look-back, one digit per thread, kLookWindow predecessors per round (their
@@ -517,11 +523,20 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
             if (!stored) {
                 if (FAST) c.dst[out_idx[i]] = k; else c.dst[(int64_t)out_idx[i] * c.dst_stride] = k;
             }
+            if constexpr (L::SPLIT) {  // the value travels with its key
+                bool vstored = false;
+                if constexpr (Digit::kUsesIndex) {
+                    if (dg.bucket_values) {
+                        reinterpret_cast<V *>(dg.bucket_values[d])[out_idx[i]] = svals[p];
+                        vstored = true;
+                    }
+                }
+                if (!vstored) c.vdst[out_idx[i]] = svals[p];
+            }
         }
     }
 
-    if constexpr (HAS_VALUES) {
-        V *svals = reinterpret_cast<V *>(smem_raw);
+    if constexpr (HAS_VALUES && !L::SPLIT) {
         __syncthreads();  // every key has left the staging buffer
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {

@@ -121,3 +121,28 @@ def test_config5_reduce_and_inclusive_scan_float32_2_30(accelerator):
     mid = (n // 2 // chunk) * chunk
     truth = ends[mid // chunk - 1] + torch.cumsum(x[mid:mid + chunk].double(), 0)
     assert float((out[mid:mid + chunk].double() - truth).abs().max()) <= tol
+
+
+def test_more_than_2_30_keys_use_the_wide_look_back_words(accelerator):
+    # from 2^30 keys on, the per-digit tile counts no longer fit 30 bits: the 64-bit status path
+    n = (1 << 30) + 12345
+    keys = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=torch.Generator("cuda").manual_seed(9))
+    hist = torch.zeros(256, dtype=torch.int64, device="cuda")
+    chunk = 1 << 28
+    for i in range(0, n, chunk):
+        hist += torch.bincount(keys[i:i + chunk].to(torch.int64), minlength=256)
+    op = Sorts.AscendingUInt8
+    temp = accelerator.Allocate1D(accelerator.ComputeRadixSortTempStorageSize(op, n), torch.int32)
+    accelerator.CreateRadixSort(op)(None, keys, temp)
+    accelerator.CheckDeviceStatus(None, temp)
+    # a sorted array of bytes is the run-length expansion of its histogram
+    ends = torch.cumsum(hist, 0)
+    starts = ends - hist
+    for d in (0, 1, 17, 128, 254, 255):
+        a, b = int(starts[d]), int(ends[d])
+        if b > a:
+            assert int(keys[a]) == d and int(keys[b - 1]) == d
+            if a > 0:
+                assert int(keys[a - 1]) < d
+    probe = keys[::4099].to(torch.int16)
+    assert bool((probe[1:] >= probe[:-1]).all())
