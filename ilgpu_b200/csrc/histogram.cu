@@ -13,64 +13,66 @@ constexpr int kHistWarps = kHistThreads / 32;
 constexpr int64_t kHistSmemBytes = 48 * 1024;  // static limit, no opt-in needed
 
 struct LocParams {
-    double lo_d, scale_d;
-    float lo_f, scale_f;
+    double lo_d, scale_d, bins_d;  // bins_* = num_bins as a floating-point value
+    float lo_f, scale_f, bins_f;
     long long num_bins;
+    int last;  // num_bins - 1
 };
 
 // ---- bin locators ---------------------------------------------------------------------
+// run() returns the bin as an int (the bin count is below 2^31); kInRange = the result needs
+// no bounds check.
 template <typename T, int LOCATOR> struct Locate;
 
 template <> struct Locate<float, B200ALG_LOCATOR_EQUAL_WIDTH_CLAMP> {
-    static __device__ __forceinline__ long long run(float x, const LocParams &p) {
-        const float t = (x - p.lo_f) * p.scale_f;
-        if (t != t) return 0;
-        int b = __float2int_rd(t);  // saturating
-        const int last = (int)p.num_bins - 1;
-        b = b < 0 ? 0 : (b > last ? last : b);
-        return b;
+    static constexpr bool kInRange = true;
+    static __device__ __forceinline__ int run(float x, const LocParams &p) {
+        // floor, then clamp == clamp, then truncate; fmaxf(NaN, 0) = 0 sends NaN to bin 0
+        const float t = fminf(fmaxf((x - p.lo_f) * p.scale_f, 0.0f), p.bins_f);
+        return min(__float2int_rz(t), p.last);
     }
 };
 template <typename T> struct Locate<T, B200ALG_LOCATOR_EQUAL_WIDTH_CLAMP> {
-    static __device__ __forceinline__ long long run(T x, const LocParams &p) {
-        const double t = ((double)x - p.lo_d) * p.scale_d;
-        if (t != t) return 0;
-        const double f = floor(t);
-        if (f < 0.0) return 0;
-        if (f >= (double)p.num_bins) return p.num_bins - 1;
-        return (long long)f;
+    static constexpr bool kInRange = true;
+    static __device__ __forceinline__ int run(T x, const LocParams &p) {
+        const double t = fmin(fmax(((double)x - p.lo_d) * p.scale_d, 0.0), p.bins_d);
+        return min(__double2int_rz(t), p.last);
     }
 };
 template <> struct Locate<int32_t, B200ALG_LOCATOR_MODULO> {
-    static __device__ __forceinline__ long long run(int32_t x, const LocParams &p) {
-        long long r = (long long)x % p.num_bins;
+    static constexpr bool kInRange = true;
+    static __device__ __forceinline__ int run(int32_t x, const LocParams &p) {
+        const int r = x % (int)p.num_bins;
         return r < 0 ? -r : r;
     }
 };
 template <> struct Locate<int64_t, B200ALG_LOCATOR_MODULO> {
-    static __device__ __forceinline__ long long run(int64_t x, const LocParams &p) {
-        long long r = (long long)x % p.num_bins;
-        return r < 0 ? -r : r;
+    static constexpr bool kInRange = true;
+    static __device__ __forceinline__ int run(int64_t x, const LocParams &p) {
+        const long long r = (long long)x % p.num_bins;
+        return (int)(r < 0 ? -r : r);
     }
 };
 template <> struct Locate<uint32_t, B200ALG_LOCATOR_MODULO> {
-    static __device__ __forceinline__ long long run(uint32_t x, const LocParams &p) {
-        return (long long)(x % (unsigned long long)p.num_bins);
-    }
+    static constexpr bool kInRange = true;
+    static __device__ __forceinline__ int run(uint32_t x, const LocParams &p) { return (int)(x % (unsigned int)p.num_bins); }
 };
 template <> struct Locate<uint64_t, B200ALG_LOCATOR_MODULO> {
-    static __device__ __forceinline__ long long run(uint64_t x, const LocParams &p) {
-        return (long long)(x % (unsigned long long)p.num_bins);
+    static constexpr bool kInRange = true;
+    static __device__ __forceinline__ int run(uint64_t x, const LocParams &p) {
+        return (int)(x % (unsigned long long)p.num_bins);
     }
 };
 template <> struct Locate<float, B200ALG_LOCATOR_MODULO> {
-    static __device__ __forceinline__ long long run(float x, const LocParams &p) {
-        return (long long)(int)fabsf(fmodf(x, (float)p.num_bins));
+    static constexpr bool kInRange = false;
+    static __device__ __forceinline__ int run(float x, const LocParams &p) {
+        return (int)fabsf(fmodf(x, (float)p.num_bins));
     }
 };
 template <> struct Locate<double, B200ALG_LOCATOR_MODULO> {
-    static __device__ __forceinline__ long long run(double x, const LocParams &p) {
-        return (long long)(int)fabs(fmod(x, (double)p.num_bins));
+    static constexpr bool kInRange = false;
+    static __device__ __forceinline__ int run(double x, const LocParams &p) {
+        return (int)fabs(fmod(x, (double)p.num_bins));
     }
 };
 
@@ -140,13 +142,13 @@ histogram_smem_kernel(const T *__restrict__ in, int64_t stride, int64_t n, LocPa
             b.u = __ldcs(vin + i + step);
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
-                const long long ba = Locate<T, LOCATOR>::run(a.t[k], p);
-                if ((unsigned long long)ba < (unsigned long long)nb) atomicAdd(mine + (ba << rshift), 1u);
+                const int ba = Locate<T, LOCATOR>::run(a.t[k], p);
+                if (Locate<T, LOCATOR>::kInRange || (unsigned int)ba < (unsigned int)nb) atomicAdd(mine + (ba << rshift), 1u);
             }
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
-                const long long bb = Locate<T, LOCATOR>::run(b.t[k], p);
-                if ((unsigned long long)bb < (unsigned long long)nb) atomicAdd(mine + (bb << rshift), 1u);
+                const int bb = Locate<T, LOCATOR>::run(b.t[k], p);
+                if (Locate<T, LOCATOR>::kInRange || (unsigned int)bb < (unsigned int)nb) atomicAdd(mine + (bb << rshift), 1u);
             }
         }
         for (; i < nvec; i += step) {
@@ -154,24 +156,24 @@ histogram_smem_kernel(const T *__restrict__ in, int64_t stride, int64_t n, LocPa
             a.u = __ldcs(vin + i);
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
-                const long long ba = Locate<T, LOCATOR>::run(a.t[k], p);
-                if ((unsigned long long)ba < (unsigned long long)nb) atomicAdd(mine + (ba << rshift), 1u);
+                const int ba = Locate<T, LOCATOR>::run(a.t[k], p);
+                if (Locate<T, LOCATOR>::kInRange || (unsigned int)ba < (unsigned int)nb) atomicAdd(mine + (ba << rshift), 1u);
             }
         }
         if (blockIdx.x == 0) {
             for (int64_t j = threadIdx.x; j < head; j += kHistThreads) {
-                const long long b = Locate<T, LOCATOR>::run(in[j], p);
-                if ((unsigned long long)b < (unsigned long long)nb) atomicAdd(mine + (b << rshift), 1u);
+                const int b = Locate<T, LOCATOR>::run(in[j], p);
+                if (Locate<T, LOCATOR>::kInRange || (unsigned int)b < (unsigned int)nb) atomicAdd(mine + (b << rshift), 1u);
             }
             for (int64_t j = tail + threadIdx.x; j < n; j += kHistThreads) {
-                const long long b = Locate<T, LOCATOR>::run(in[j], p);
-                if ((unsigned long long)b < (unsigned long long)nb) atomicAdd(mine + (b << rshift), 1u);
+                const int b = Locate<T, LOCATOR>::run(in[j], p);
+                if (Locate<T, LOCATOR>::kInRange || (unsigned int)b < (unsigned int)nb) atomicAdd(mine + (b << rshift), 1u);
             }
         }
     } else {
         for (int64_t i = gtid; i < n; i += step) {
-            const long long b = Locate<T, LOCATOR>::run(in[i * stride], p);
-            if ((unsigned long long)b < (unsigned long long)nb) atomicAdd(mine + (b << rshift), 1u);
+            const int b = Locate<T, LOCATOR>::run(in[i * stride], p);
+            if (Locate<T, LOCATOR>::kInRange || (unsigned int)b < (unsigned int)nb) atomicAdd(mine + (b << rshift), 1u);
         }
     }
     __syncthreads();
@@ -193,8 +195,8 @@ histogram_global_kernel(const T *__restrict__ in, int64_t stride, int64_t n, Loc
     bool of = false;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
-        const long long b = Locate<T, LOCATOR>::run(in[i * stride], p);
-        if ((unsigned long long)b < (unsigned long long)p.num_bins) of |= add_to_bin(bins, b, 1ull, bin_dtype);
+        const int b = Locate<T, LOCATOR>::run(in[i * stride], p);
+        if (Locate<T, LOCATOR>::kInRange || (unsigned int)b < (unsigned int)p.num_bins) of |= add_to_bin(bins, b, 1ull, bin_dtype);
     }
     if (overflow && __syncthreads_or(of) && threadIdx.x == 0) atomicOr(overflow, 1);
 }
@@ -260,6 +262,9 @@ extern "C" int b200alg_histogram(void *stream, const void *in, int64_t stride, i
     p.scale_d = (double)num_bins / (hi - lo);
     p.lo_f = (float)lo;
     p.scale_f = (float)num_bins / ((float)hi - (float)lo);
+    p.bins_d = (double)num_bins;
+    p.bins_f = (float)num_bins;
+    p.last = (int)(num_bins - 1);
     cudaStream_t s = (cudaStream_t)stream;
     switch (in_dtype) {
     case B200ALG_I32: return dispatch_locator<int32_t>(s, in, stride, n, locator, p, bins, bin_dtype, overflow);
