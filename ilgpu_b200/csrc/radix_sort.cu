@@ -226,19 +226,10 @@ struct NoValue {};
 template <typename V> struct ValueBytes { static constexpr int value = sizeof(V); };
 template <> struct ValueBytes<NoValue> { static constexpr int value = 0; };
 
-// Lanes of a warp that hold the same 8-bit digit: one ballot per digit bit (the hardware
-// match instruction serialises over the distinct values, ~30 of them for random digits).
-__device__ __forceinline__ unsigned int match_digit(unsigned int digit) {
-    unsigned int differs = 0u;  // lanes whose digit differs from this lane's in some bit
-#pragma unroll
-    for (int b = 0; b < 8; ++b) {
-        const bool bit = (digit & (1u << b)) != 0u;
-        const unsigned int m = __ballot_sync(0xffffffffu, bit);
-        const unsigned int ext = bit ? 0xffffffffu : 0u;
-        differs |= m ^ ext;
-    }
-    return ~differs;
-}
+#ifndef B200ALG_RANK_GROUP
+#define B200ALG_RANK_GROUP 1
+#endif
+constexpr int kRankGroup = B200ALG_RANK_GROUP;  // items ranked together, each with a mask table of its own (1, 2 or 4)
 
 template <typename K, typename V, bool KEEP_DIGITS, int THREADS, int ITEMS>
 struct OnesweepSmem {
@@ -248,13 +239,15 @@ struct OnesweepSmem {
     // SM; otherwise the values reuse the keys' staging buffer in a second round
     static constexpr bool SPLIT = VB != 0 && (size_t)TILE * ((int)sizeof(K) + VB) <= 72 * 1024;
     static constexpr int STAGE = SPLIT ? (int)sizeof(K) + VB : ((int)sizeof(K) > VB ? (int)sizeof(K) : VB);
-    static constexpr size_t bytes = (size_t)TILE * STAGE + (size_t)(THREADS / 32) * kRadix * 8 + kRadix * 4 * 2 + 64 +
-                                    (KEEP_DIGITS ? (size_t)TILE + kRadix * 16 : 0);
+    static constexpr size_t base_bytes = (size_t)TILE * STAGE + (size_t)(THREADS / 32) * kRadix * 8 + kRadix * 4 * 2 + 64 +
+                                         (KEEP_DIGITS ? (size_t)TILE + kRadix * 16 : 0);
+    // mask tables: #0 beside the counts, #1 after everything else, #2 and #3 in the staging
+    // buffer, which is idle while a tile is ranked
+    static constexpr size_t mask_bytes = (size_t)(THREADS / 32) * kRadix * 4;
+    static constexpr size_t bytes = base_bytes + (kRankGroup >= 2 ? mask_bytes : 0);
+    static_assert(kRankGroup <= 2 || (size_t)TILE * STAGE >= (kRankGroup - 2) * mask_bytes, "staging too small for the mask tables");
 };
 
-#ifndef B200ALG_BALLOT_ITEMS
-#define B200ALG_BALLOT_ITEMS 4
-#endif
 #ifndef B200ALG_LOOK_WINDOW
 #define B200ALG_LOOK_WINDOW 4
 #endif
@@ -328,14 +321,15 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
     constexpr int WARPS = THREADS / 32;
     constexpr int TILE = THREADS * ITEMS;
     constexpr bool HAS_VALUES = ValueBytes<V>::value != 0;
-    constexpr int BALLOT_ITEMS = B200ALG_BALLOT_ITEMS < ITEMS ? B200ALG_BALLOT_ITEMS : ITEMS;
     constexpr int kLookWindow = B200ALG_LOOK_WINDOW;  // predecessors examined per look-back round
     using S = StatusWord<SW>;
     using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
     K *skeys = reinterpret_cast<K *>(smem_raw);
-    // [WARPS][256] entries {x: count, later offset, of the digit in the warp; y: lanes that hold the digit}
-    uint2 *warp_tbl = reinterpret_cast<uint2 *>(smem_raw + (size_t)TILE * L::STAGE);
-    unsigned int *bin_excl = reinterpret_cast<unsigned int *>(warp_tbl + WARPS * kRadix);  // digit's first slot inside the tile
+    // warp_tbl[w][d]: count, later offset, of digit d in warp w; mask_tbl[w][d]: lanes of warp w
+    // that hold d in the item being ranked (zero between items)
+    unsigned int *warp_tbl = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE);
+    unsigned int *mask_tbl = warp_tbl + WARPS * kRadix;
+    unsigned int *bin_excl = mask_tbl + WARPS * kRadix;  // digit's first slot inside the tile
     unsigned int *bin_goff = bin_excl + kRadix;            // global index of slot p is bin_goff[d] + p
     unsigned int *misc = bin_goff + kRadix;                // [1..8] warp sums
     unsigned char *sdigit = reinterpret_cast<unsigned char *>(misc + 16);  // only when digits need the index
@@ -347,18 +341,23 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
 
     {
         uint4 *z = reinterpret_cast<uint4 *>(warp_tbl);
-        for (int i = tid; i < WARPS * kRadix / 2; i += THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+        for (int i = tid; i < WARPS * kRadix / 4; i += THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (kRankGroup > 2) {  // the mask tables that live in the staging buffer
+            uint4 *zs = reinterpret_cast<uint4 *>(smem_raw);
+            for (int i = tid; i < (kRankGroup - 2) * WARPS * kRadix / 4; i += THREADS) zs[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
     __syncthreads();
     B200ALG_STAMP(0);
 
     // Ranking inside the warp: for every item, the lanes that hold the same digit have to find
-    // each other; the lowest of them advances the warp's count of that digit.  Two methods are
-    // interleaved so that neither the integer pipe nor shared memory saturates:
-    //  - ballots: one vote per digit bit, combined in registers;
-    //  - table:   every lane ORs its bit into the digit's mask in the warp's table and reads
-    //             the mask back after a warp barrier.
-    // After the loop the x fields of the warp's table hold its digit counts.
+    // each other.  Every lane ORs its bit into the digit's mask in the warp's table and reads
+    // the mask back after a warp barrier; the lowest lane of the mask adds the number of its
+    // lanes to the warp's count of that digit, clears the mask and hands the previous count to
+    // the others.  kRankGroup items go through these steps together, each with a mask table of
+    // its own, so that a group costs three trips to shared memory instead of three per item.
+    // (Finding the peers with one vote per digit bit, or with the hardware match instruction,
+    // measured slower than the table.)  After the loop the warp's table holds its digit counts.
     V val[HAS_VALUES ? ITEMS : 1];
     if constexpr (HAS_VALUES) {  // requested now, needed after the ranking
 #pragma unroll
@@ -369,36 +368,50 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
     }
     V *svals = reinterpret_cast<V *>(smem_raw + (L::SPLIT ? (size_t)TILE * sizeof(K) : 0));
 
-    uint2 *my_tbl = warp_tbl + warp * kRadix;
+    unsigned int *my_tbl = warp_tbl + warp * kRadix;
+    unsigned int *my_mask[kRankGroup];
+#pragma unroll
+    for (int g = 0; g < kRankGroup; ++g) {
+        unsigned int *table = g == 0   ? mask_tbl
+                              : g == 1 ? reinterpret_cast<unsigned int *>(smem_raw + L::base_bytes)
+                                       : reinterpret_cast<unsigned int *>(smem_raw) + (g - 2) * WARPS * kRadix;
+        my_mask[g] = table + warp * kRadix;
+    }
     const unsigned int lt = lanemask_lt();
     const unsigned int my_bit = 1u << lane;
     unsigned int packed[ITEMS];  // (rank among the warp's keys of that digit) << 8 | digit
+    static_assert(ITEMS % kRankGroup == 0, "items are ranked in whole groups");
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-        unsigned int d;
-        if (FAST) {
-            d = dg(key[i], tile_base + warp_base + i * 32);
-        } else {
-            const int local = warp_base + i * 32;
-            d = local < valid ? dg(key[i], tile_base + local) : 0xFFu;  // padding ranks behind every real key
+    for (int i0 = 0; i0 < ITEMS; i0 += kRankGroup) {
+        unsigned int d[kRankGroup], peers[kRankGroup], count[kRankGroup];
+#pragma unroll
+        for (int g = 0; g < kRankGroup; ++g) {
+            const int i = i0 + g;
+            if (FAST) {
+                d[g] = dg(key[i], tile_base + warp_base + i * 32);
+            } else {
+                const int local = warp_base + i * 32;
+                d[g] = local < valid ? dg(key[i], tile_base + local) : 0xFFu;  // padding ranks behind every real key
+            }
+            atomicOr(&my_mask[g][d[g]], my_bit);
         }
-        if ((i * BALLOT_ITEMS) / ITEMS != ((i + 1) * BALLOT_ITEMS) / ITEMS) {  // BALLOT_ITEMS of ITEMS, evenly spread
-            const unsigned int peers = match_digit(d);
-            const unsigned int before = peers & lt;
-            const unsigned int count = my_tbl[d].x;
-            __syncwarp();
-            if (before == 0u) my_tbl[d].x = count + (unsigned int)__popc(peers);
-            packed[i] = ((count + (unsigned int)__popc(before)) << 8) | d;
-            __syncwarp();
-        } else {
-            atomicOr(&my_tbl[d].y, my_bit);
-            __syncwarp();
-            const uint2 e = my_tbl[d];
-            __syncwarp();
-            const unsigned int before = e.y & lt;
-            if (before == 0u) my_tbl[d] = make_uint2(e.x + (unsigned int)__popc(e.y), 0u);
-            packed[i] = ((e.x + (unsigned int)__popc(before)) << 8) | d;
-            __syncwarp();
+        __syncwarp();
+#pragma unroll
+        for (int g = 0; g < kRankGroup; ++g) peers[g] = my_mask[g][d[g]];
+        __syncwarp();
+#pragma unroll
+        for (int g = 0; g < kRankGroup; ++g) {
+            count[g] = 0u;
+            if ((peers[g] & lt) == 0u) {  // lowest lane with this digit
+                count[g] = atomicAdd(&my_tbl[d[g]], (unsigned int)__popc(peers[g]));
+                my_mask[g][d[g]] = 0u;
+            }
+            __syncwarp();  // the counts advance item by item
+        }
+#pragma unroll
+        for (int g = 0; g < kRankGroup; ++g) {
+            count[g] = __shfl_sync(0xffffffffu, count[g], __ffs(peers[g]) - 1);
+            packed[i0 + g] = ((count[g] + (unsigned int)__popc(peers[g] & lt)) << 8) | d[g];
         }
     }
     B200ALG_STAMP(1);
@@ -412,8 +425,8 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
         unsigned int run = 0;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const unsigned int cnt = warp_tbl[w * kRadix + tid].x;
-            warp_tbl[w * kRadix + tid].x = run;
+            const unsigned int cnt = warp_tbl[w * kRadix + tid];
+            warp_tbl[w * kRadix + tid] = run;
             run += cnt;
         }
         tile_count = run;
@@ -438,7 +451,7 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
         bin_excl[tid] = excl;
         // fold the digit's first slot into the per-warp offsets: one table lookup per key
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) warp_tbl[w * kRadix + tid].x += excl;
+        for (int w = 0; w < WARPS; ++w) warp_tbl[w * kRadix + tid] += excl;
     }
     __syncthreads();
     B200ALG_STAMP(4);
@@ -448,7 +461,7 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const unsigned int d = packed[i] & 0xFFu;
-        pos[i] = (packed[i] >> 8) + my_tbl[d].x;
+        pos[i] = (packed[i] >> 8) + my_tbl[d];
         skeys[pos[i]] = key[i];
         if constexpr (Digit::kUsesIndex) sdigit[pos[i]] = (unsigned char)d;
         if constexpr (L::SPLIT) svals[pos[i]] = val[i];
@@ -567,7 +580,7 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
 // Persistent blocks: block b works on tiles b, b + gridDim.x, ...; the grid is sized so that all
 // blocks are resident at once, hence a tile only ever waits for tiles that already run.
 template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS>
-__global__ void __launch_bounds__(THREADS, B200ALG_ONESWEEP_MIN_BLOCKS)
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, int pass, Digit dg,
                 TempHeader *hdr, const unsigned int *gbase_all, SW *status_all, int num_tiles) {
     constexpr int TILE = THREADS * ITEMS;
@@ -603,6 +616,14 @@ onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, 
 
     int tile = (int)blockIdx.x;
     if (tile >= num_tiles) return;
+    {   // the lane masks of the ranking tables start at zero and are left at zero by every item
+        unsigned int *mask0 = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE) + (THREADS / 32) * kRadix;
+        unsigned int *mask1 = reinterpret_cast<unsigned int *>(smem_raw + L::base_bytes);
+        for (int i = threadIdx.x; i < (THREADS / 32) * kRadix; i += THREADS) {
+            mask0[i] = 0u;
+            if (kRankGroup >= 2) mask1[i] = 0u;
+        }
+    }
     K key[ITEMS];
     load_tile_keys<K, V, SW, THREADS, ITEMS>(key, c, tile);
     while (true) {
