@@ -201,22 +201,34 @@ template <typename K> struct SplitterBucket {
     void *const *bucket_keys;
     void *const *bucket_values;
     // Copies the splitters into shared memory (keys already transformed) and reads them from
-    // there afterwards.  Call with all threads of the block, then synchronise.
+    // there afterwards; slots up to kSmall are padded with the largest key, which no key
+    // exceeds.  Call with all threads of the block, then synchronise.
+    static constexpr int kSmall = 7;  // up to this many splitters are compared without a loop
     __device__ __forceinline__ void stage(K *shared_keys, int64_t *shared_index) {
         for (int s = threadIdx.x; s < num_splitters; s += blockDim.x) {
             shared_keys[s] = xf(splitter_keys[s]);
             shared_index[s] = splitter_index[s];
         }
+        for (int s = num_splitters + threadIdx.x; s < kSmall; s += blockDim.x) shared_keys[s] = (K) ~(K)0;
         splitter_keys = shared_keys;
         splitter_index = shared_index;
     }
     __device__ __forceinline__ unsigned int operator()(K key, int64_t local_index) const {
         const K tk = xf(key);
-        const int64_t gi = index_base + local_index;
+        // The splitters ascend by (key, index): count those with a smaller key, then walk over
+        // the (rare) ones with an equal key whose index does not exceed this element's.
         unsigned int b = 0;
-        for (int s = 0; s < num_splitters; ++s) {
-            const K sk = splitter_keys[s];
-            b += (sk < tk) || (sk == tk && splitter_index[s] <= gi);
+        if (num_splitters == 1) {
+            b = splitter_keys[0] < tk;
+        } else if (num_splitters <= kSmall) {
+#pragma unroll
+            for (int s = 0; s < kSmall; ++s) b += splitter_keys[s] < tk;
+        } else {
+            for (int s = 0; s < num_splitters; ++s) b += splitter_keys[s] < tk;
+        }
+        if ((int)b < num_splitters && splitter_keys[b] == tk) {
+            const int64_t gi = index_base + local_index;
+            while ((int)b < num_splitters && splitter_keys[b] == tk && splitter_index[b] <= gi) ++b;
         }
         return b;
     }
@@ -789,6 +801,10 @@ static int dispatch_key(cudaStream_t s, int key_bytes, void *keys, int64_t strid
 }
 
 // ---- 5. stable partition of a shard into per-rank buckets (multi-GPU sort) ---------------
+// Bucket sizes of a shard.  With at most eight buckets (one per rank) every thread counts in
+// a register, one byte per bucket, and empties it into 32-bit totals before a byte can wrap;
+// the totals are added up per warp by shuffles and per block in shared memory.  More buckets
+// than that are counted with shared-memory atomics on tables private to each warp.
 template <typename K>
 __global__ void __launch_bounds__(256)
 bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K> dg, unsigned int *ghist) {
@@ -800,7 +816,61 @@ bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K>
     __syncthreads();
     unsigned int *mine = sh[threadIdx.x >> 5];
     const int64_t step = (int64_t)gridDim.x * 256;
-    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += step) atomicAdd(mine + dg(keys[i], i), 1u);
+    const int64_t gtid = (int64_t)blockIdx.x * 256 + threadIdx.x;
+
+    if (dg.num_splitters < 8) {
+        constexpr int VEC = 16 / (int)sizeof(K);
+        union Pack { uint4 u; K k[VEC]; };
+        int64_t head = (int64_t)(((16u - (unsigned)((uintptr_t)keys & 15u)) & 15u) / sizeof(K));
+        if (head > n) head = n;
+        const uint4 *vin = reinterpret_cast<const uint4 *>(keys + head);
+        const int64_t nvec = (n - head) / VEC;
+        const int64_t tail = head + nvec * VEC;
+        unsigned long long bytes = 0ull;  // byte b = keys of bucket b since the last flush
+        unsigned int total[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        int pending = 0;
+        auto flush = [&]() {
+#pragma unroll
+            for (int b = 0; b < 8; ++b) total[b] += (unsigned int)(bytes >> (8 * b)) & 0xFFu;
+            bytes = 0ull;
+            pending = 0;
+        };
+        int64_t v = gtid;
+        for (; v + step < nvec; v += 2 * step) {
+            Pack a, b;
+            a.u = __ldcs(vin + v);
+            b.u = __ldcs(vin + v + step);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(a.k[k], head + v * VEC + k));
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(b.k[k], head + (v + step) * VEC + k));
+            pending += 2 * VEC;
+            if (pending > 255 - 2 * VEC) flush();
+        }
+        for (; v < nvec; v += step) {
+            Pack a;
+            a.u = __ldcs(vin + v);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(a.k[k], head + v * VEC + k));
+            pending += VEC;
+            if (pending > 255 - 2 * VEC) flush();
+        }
+        flush();
+        if (blockIdx.x == 0) {  // the unaligned ends: fewer than 16 bytes each
+            if (threadIdx.x < head) total[dg(keys[threadIdx.x], threadIdx.x)] += 1u;
+            const int64_t j = tail + threadIdx.x;
+            if (j < n) total[dg(keys[j], j)] += 1u;
+        }
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            unsigned int t = total[b];
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) t += __shfl_down_sync(0xffffffffu, t, d);
+            if ((threadIdx.x & 31) == 0 && t) mine[b] = t;
+        }
+    } else {
+        for (int64_t i = gtid; i < n; i += step) atomicAdd(mine + dg(keys[i], i), 1u);
+    }
     __syncthreads();
     unsigned int c = 0;
 #pragma unroll
