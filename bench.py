@@ -6,8 +6,8 @@ beside it) on 1..8 B200s.
 
 N = 1: one step = one ascending RadixSort of 2^26 uint32 keys (i.i.d. uniform, seeded).
 N > 1 (under torchrun, one rank per GPU): one step = one sample sort of N * 2^26 keys,
-2^26 per GPU (weak scaling): sampled splitters, stable partition, NCCL all-to-all of the
-buckets, local radix sort.
+2^26 per GPU (weak scaling): sampled splitters, a stable partition whose kernel stores every
+bucket straight into its owner's receive buffer (peer memory over NVLink), local radix sort.
 `--impl reference` times the CPU restatement of the reference's CPUAccelerator sort on the
 host cores (the reference is C#; no .NET toolchain exists on these machines).
 
@@ -500,7 +500,7 @@ def run_native(args) -> None:
         "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": {
             "workload": "RadixSort ascending, 2^26 uint32 keys per GPU, i.i.d. uniform over the full range (seeded), "
-                        "4 digit passes of 8 bits" + ("" if world == 1 else "; sample sort across GPUs with NCCL all-to-all"),
+                        "4 digit passes of 8 bits" + ("" if world == 1 else "; sample sort across GPUs, buckets exchanged by peer stores from the partition kernel"),
             "keys_per_gpu": n, "total_keys": world * n,
             "l2": "inputs larger than L2: 256 MiB per step, a fresh unsorted buffer each step",
         },

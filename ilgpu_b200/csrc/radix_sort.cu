@@ -66,26 +66,31 @@ static bool key_xform_constants(int dtype, int order, uint64_t &xn, uint64_t &xp
 }
 
 // ---- 1. histograms of all digit positions ----------------------------------------------
-constexpr int kHistoThreads = 512;
-constexpr int kHistoReplicas = 8;  // counters per (digit position, digit): lane l uses replica l % 8
+constexpr int kHistoThreads = 1024;
+// Counters per (digit position, digit): lane l uses replica l % replicas.  With 32 replicas
+// every lane of a warp has a bank of its own and an atomic instruction is one wavefront
+// whatever the digits are; that table (128 KB for 4-byte keys) takes one block per SM, so
+// short inputs use 8 replicas and two blocks per SM instead.
+constexpr int kHistoMaxSmem = 128 * 1024;
 
 template <typename K>
 __global__ void __launch_bounds__(kHistoThreads)
-sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, KeyXform<K> xf, unsigned int *ghist) {
+sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, KeyXform<K> xf, unsigned int *ghist, int rshift) {
     constexpr int P = sizeof(K);
     // replicas are interleaved ([position][digit][replica]) so that the lanes of a warp spread
     // over the banks even when their digits collide
-    extern __shared__ unsigned int sh[];  // P x 256 x kHistoReplicas
-    for (int i = threadIdx.x; i < kHistoReplicas * P * kRadix; i += kHistoThreads) sh[i] = 0u;
+    extern __shared__ unsigned int sh[];  // P x 256 x replicas
+    const int replicas = 1 << rshift;
+    for (int i = threadIdx.x; i < replicas * P * kRadix; i += kHistoThreads) sh[i] = 0u;
     __syncthreads();
-    unsigned int *mine = sh + (threadIdx.x & (kHistoReplicas - 1));
+    unsigned int *mine = sh + (threadIdx.x & (replicas - 1));
     const int64_t step = (int64_t)gridDim.x * kHistoThreads;
     const int64_t gtid = (int64_t)blockIdx.x * kHistoThreads + threadIdx.x;
     auto count = [&](K raw) {
         const K b = xf(raw);
 #pragma unroll
         for (int p = 0; p < P; ++p)
-            atomicAdd(mine + ((p * kRadix + ((unsigned)(b >> (8 * p)) & 0xFFu)) * kHistoReplicas), 1u);
+            atomicAdd(mine + ((p * kRadix + ((unsigned)(b >> (8 * p)) & 0xFFu)) << rshift), 1u);
     };
     if (stride == 1) {
         constexpr int VEC = 16 / sizeof(K);
@@ -121,8 +126,7 @@ sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, Key
     __syncthreads();
     for (int i = threadIdx.x; i < P * kRadix; i += kHistoThreads) {
         unsigned int c = 0;
-#pragma unroll
-        for (int r = 0; r < kHistoReplicas; ++r) c += sh[i * kHistoReplicas + ((r + threadIdx.x) & (kHistoReplicas - 1))];
+        for (int r = 0; r < replicas; ++r) c += sh[(i << rshift) + ((r + threadIdx.x) & (replicas - 1))];
         if (c) atomicAdd(ghist + i, c);
     }
 }
@@ -740,19 +744,24 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
     {
         const int64_t per_block = (int64_t)kHistoThreads * (16 / sizeof(K)) * 2;
         int64_t want = ceil_div(n, per_block);
-        const int64_t cap = (int64_t)sm_count() * (2048 / kHistoThreads);
+        int rshift = 3;
+        if (n >= (1ll << 22)) {
+            rshift = 5;
+            while (((size_t)sizeof(K) * kRadix * sizeof(unsigned int) << rshift) > (size_t)kHistoMaxSmem) --rshift;
+        }
+        const size_t histo_smem = (size_t)sizeof(K) * kRadix * sizeof(unsigned int) << rshift;
+        const int64_t cap = (int64_t)sm_count() * (histo_smem > 100 * 1024 ? 1 : 2);
         const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-        constexpr size_t histo_smem = sizeof(K) * kRadix * kHistoReplicas * sizeof(unsigned int);
-        if (histo_smem > 48 * 1024) {
+        {
             static thread_local int histo_device = -1;
             int dev = 0;
             B200ALG_CUDA_TRY(cudaGetDevice(&dev));
             if (histo_device != dev) {
-                B200ALG_CUDA_TRY(cudaFuncSetAttribute(sort_histogram_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)histo_smem));
+                B200ALG_CUDA_TRY(cudaFuncSetAttribute(sort_histogram_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistoMaxSmem));
                 histo_device = dev;
             }
         }
-        sort_histogram_kernel<K><<<blocks, kHistoThreads, histo_smem, s>>>(keys, stride, n, xf, ghist);
+        sort_histogram_kernel<K><<<blocks, kHistoThreads, histo_smem, s>>>(keys, stride, n, xf, ghist, rshift);
         B200ALG_LAUNCH_CHECK();
     }
     sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, L.passes, (unsigned int)n);
