@@ -4,7 +4,7 @@
 //   2. a one-block kernel turns them into global digit offsets and finds digit positions
 //      on which every key agrees (those passes are skipped),
 //   3. one kernel per remaining digit position: a tile of keys is ranked in shared memory
-//      (warp match / ballot), the tile's digit counts are chained to the previous tiles'
+//      (the lanes of a warp meet in per-warp digit tables), the tile's digit counts are chained to the previous tiles'
 //      with decoupled look-back, and the tile is scattered to its final place for that
 //      digit - each key is read once and written once per pass.
 //
