@@ -468,7 +468,7 @@ def run_native(args) -> None:
             torch.cuda.synchronize()
             return start.elapsed_time(end) / k
         piped_region(2)
-        piped_steps = max(4, e2e_steps)
+        piped_steps = max(16, 2 * e2e_steps)
         e2e_ms = piped_region(piped_steps)
         for b in range(2):   # both results are complete and sorted
             ho = host_out2[b].view(torch.int32)

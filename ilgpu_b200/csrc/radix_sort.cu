@@ -73,10 +73,11 @@ constexpr int kHistoThreads = 1024;
 // short inputs use 8 replicas and two blocks per SM instead.
 constexpr int kHistoMaxSmem = 128 * 1024;
 
-template <typename K>
+template <typename K, int RSHIFT>
 __global__ void __launch_bounds__(kHistoThreads)
-sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, KeyXform<K> xf, unsigned int *ghist, int rshift) {
+sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, KeyXform<K> xf, unsigned int *ghist) {
     constexpr int P = sizeof(K);
+    constexpr int rshift = RSHIFT;
     // replicas are interleaved ([position][digit][replica]) so that the lanes of a warp spread
     // over the banks even when their digits collide
     extern __shared__ unsigned int sh[];  // P x 256 x replicas
@@ -744,12 +745,10 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
     {
         const int64_t per_block = (int64_t)kHistoThreads * (16 / sizeof(K)) * 2;
         int64_t want = ceil_div(n, per_block);
-        int rshift = 3;
-        if (n >= (1ll << 22)) {
-            rshift = 5;
-            while (((size_t)sizeof(K) * kRadix * sizeof(unsigned int) << rshift) > (size_t)kHistoMaxSmem) --rshift;
-        }
-        const size_t histo_smem = (size_t)sizeof(K) * kRadix * sizeof(unsigned int) << rshift;
+        // 32 counter replicas for long inputs (16 for 8-byte keys: 128 KB either way), else 8
+        constexpr int kBigShift = sizeof(K) == 8 ? 4 : 5;
+        const bool big = n >= (1ll << 22);
+        const size_t histo_smem = (size_t)sizeof(K) * kRadix * sizeof(unsigned int) << (big ? kBigShift : 3);
         const int64_t cap = (int64_t)sm_count() * (histo_smem > 100 * 1024 ? 1 : 2);
         const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
         {
@@ -757,11 +756,15 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
             int dev = 0;
             B200ALG_CUDA_TRY(cudaGetDevice(&dev));
             if (histo_device != dev) {
-                B200ALG_CUDA_TRY(cudaFuncSetAttribute(sort_histogram_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistoMaxSmem));
+                B200ALG_CUDA_TRY(cudaFuncSetAttribute(sort_histogram_kernel<K, kBigShift>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistoMaxSmem));
+                B200ALG_CUDA_TRY(cudaFuncSetAttribute(sort_histogram_kernel<K, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistoMaxSmem));
                 histo_device = dev;
             }
         }
-        sort_histogram_kernel<K><<<blocks, kHistoThreads, histo_smem, s>>>(keys, stride, n, xf, ghist, rshift);
+        if (big)
+            sort_histogram_kernel<K, kBigShift><<<blocks, kHistoThreads, histo_smem, s>>>(keys, stride, n, xf, ghist);
+        else
+            sort_histogram_kernel<K, 3><<<blocks, kHistoThreads, histo_smem, s>>>(keys, stride, n, xf, ghist);
         B200ALG_LAUNCH_CHECK();
     }
     sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, L.passes, (unsigned int)n);
