@@ -30,7 +30,7 @@ KEYS_PER_GPU = 1 << 26
 SORT_BYTES_PER_KEY = 36          # 4-byte keys: one histogram read + 4 x (read + write)
 SEED = 2
 # dram__bytes_read.sum + dram__bytes_write.sum of one sort call of this workload, from the ncu
-# captures summarised under profiles/: histogram pass 268.7 MB + 4 digit passes x 504.4 MB
+# captures summarised under profiles/: histogram pass 272.2 MB + 4 digit passes x 502.0 MB
 SORT_DRAM_TRAFFIC_BYTES = 272.2e6 + 4 * 502.0e6
 
 
