@@ -121,32 +121,43 @@ def cpu_reference_sort(sample_keys, cores: int, repeats: int = 1):
     return sample_keys.size / best / 1e9, best
 
 
+def cpu_default_device_sort(sample_keys):
+    """The same sort the way the reference's default CPUDevice runs it: 16 groups of one
+    thread on one multiprocessor (Src/ILGPU/Runtime/CPU/CPUDevice.cs:67-77), i.e. one host
+    thread.  Returns Gkeys/s."""
+    from oracle import cpu_oracle as oracle
+    t0 = time.perf_counter()
+    oracle.radix_sort_literal_mt(sample_keys, False, 16, 1)
+    return sample_keys.size / (time.perf_counter() - t0) / 1e9
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import numpy as np
     from ilgpu_b200 import synthetic
     cores = host_cores()
-    sample = 1 << 24
-    keys = synthetic.uniform_uint32(sample * 2, SEED)
+    n = KEYS_PER_GPU
+    keys = synthetic.uniform_uint32(n, SEED)     # the same 2^26 keys the GPU arm sorts at N = 1
     times = []
     for step in range(args.warmup + args.steps):
-        part = keys[(step % 2) * sample:(step % 2 + 1) * sample]
-        _, dt = cpu_reference_sort(part, cores)
+        _, dt = cpu_reference_sort(keys, cores)
         if step >= args.warmup:
             times.append(dt)
     sec = sum(times) / len(times)
-    value = sample / sec / 1e9
+    value = n / sec / 1e9
+    single = cpu_default_device_sort(keys[: 1 << 22])
     line = {
         "impl": "reference", "metric": "radix_sort_gkeys_per_s", "value": value, "unit": "Gkeys/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": {"workload": "RadixSort ascending, 2^26 uint32 keys i.i.d. uniform (seeded)",
-                   "keys_per_gpu": KEYS_PER_GPU, "sample_keys_per_step": sample},
+                   "keys_per_gpu": KEYS_PER_GPU, "keys_per_step": n},
         "cpu_baseline": {"value": value, "unit": "Gkeys/s", "cores": cores, "kind": "port",
-                         "sample": "2^24-key slice of the 2^26-key workload per step; C restatement of "
-                                   "CPURadixSortKernel1/2 (2 bits per pass), groups spread over all host threads"},
+                         "sample": "the full 2^26-key workload per step; C restatement of CPURadixSortKernel1/2 "
+                                   "(2 bits per pass), 16 x cores groups spread over all host threads",
+                         "default_cpu_device_one_thread": {"value": single, "unit": "Gkeys/s", "cores": 1,
+                                                           "sample": "first 2^22 keys, 16 groups run by one thread"}},
         "e2e": {"value": value, "unit": "Gkeys/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -256,6 +267,14 @@ def secondary_metrics_sharded(acc, sharded, world: int, rank: int, peak_gbs: flo
         v = nbytes_total / (ms * 1e-3) / 1e9
         return {"GB/s": round(v, 1), "frac_of_measured_hbm_x_gpus": round(v / (peak_gbs * world), 4), "ms": round(ms, 4)}
 
+    import math
+
+    def gathered(value: float):
+        t = torch.tensor([value], device="cuda", dtype=torch.float64)
+        parts = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(parts, t)
+        return [float(p.item()) for p in parts]
+
     n_total = 1 << 30
     n = n_total // world
     x = synthetic.uniform_float32_device(n, 5, "cuda", start=rank * n)
@@ -264,10 +283,18 @@ def secondary_metrics_sharded(acc, sharded, world: int, rank: int, peak_gbs: flo
         sharded.Scan(x, y, Ops.AddFloat, ib.ScanKind.Inclusive)
     dist.barrier()
     out["scan_f32_inclusive_2^30_total"] = agg(8 * n_total, time_region(lambda i: sharded.Scan(x, y, Ops.AddFloat, ib.ScanKind.Inclusive), 5, stream))
+    # float64 sums of the shards: rank r's last scan element is the total of ranks 0..r; the
+    # tolerance is the stated 1e-5 * log2(n) * sum|x| (x >= 0 here)
+    shard_sums = gathered(float(x.to(torch.float64).sum().item()))
+    total = sum(shard_sums)
+    tol = 1e-5 * math.log2(n_total) * total
+    assert abs(float(y[-1].item()) - sum(shard_sums[: rank + 1])) <= tol, "sharded scan: last element of the slice is off"
+    assert abs(float(y[0].item()) - (sum(shard_sums[:rank]) + float(x[0].item()))) <= tol, "sharded scan: first element of the slice is off"
     for _ in range(3):
         sharded.Reduce(x, Ops.AddFloat)
     dist.barrier()
     out["reduce_f32_sum_2^30_total"] = agg(4 * n_total, time_region(lambda i: sharded.Reduce(x, Ops.AddFloat), 5, stream))
+    assert abs(float(sharded.Reduce(x, Ops.AddFloat).item()) - total) <= tol, "sharded reduce is off"
     del x, y
     n_total = 1 << 28
     n = n_total // world
@@ -279,7 +306,86 @@ def secondary_metrics_sharded(acc, sharded, world: int, rank: int, peak_gbs: flo
         sharded.Histogram(f, bins, ovf, loc)
     dist.barrier()
     out["histogram_f32_256bins_2^28_total"] = agg(4 * n_total, time_region(lambda i: sharded.Histogram(f, bins, ovf, loc), 5, stream))
+    # one more call into fresh bins: they sum to n and equal the bins one GPU computes for the
+    # same 2^28 values (rank 0 generates them all)
+    del f
+    f = synthetic.normal_float32_device(n, 3, "cuda", start=rank * n)
+    bins.zero_()
+    sharded.Histogram(f, bins, ovf, loc)
+    assert int(bins.to(torch.int64).sum().item()) == n_total, "sharded histogram: the bins do not sum to n"
+    if rank == 0:
+        del f
+        whole = synthetic.normal_float32_device(n_total, 3, "cuda")
+        single = torch.zeros(256, dtype=torch.int32, device="cuda")
+        acc.Histogram(None, whole, single, ovf, loc)
+        assert torch.equal(single, bins), "sharded histogram differs from the single-GPU bins"
+    out["checked"] = ("scan and reduce against float64 shard sums within 1e-5*log2(n)*sum|x|; histogram bins sum to n "
+                      "and equal the single-GPU bins")
     return out
+
+
+def _gather_variable(t, dist):
+    """All ranks' 1-D tensors of different lengths, concatenated in rank order (on every rank)."""
+    import torch
+    world = dist.get_world_size()
+    size = torch.tensor([t.numel()], device=t.device, dtype=torch.int64)
+    sizes = [torch.zeros_like(size) for _ in range(world)]
+    dist.all_gather(sizes, size)
+    sizes = [int(x.item()) for x in sizes]
+    cap = max(max(sizes), 1)
+    padded = torch.zeros(cap, dtype=t.dtype, device=t.device)
+    padded[: t.numel()] = t
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded)
+    return torch.cat([p[:k] for p, k in zip(parts, sizes)])
+
+
+def check_sharded_sort(result, checksum_in: int, n_in: int, dist) -> None:
+    """Global properties of a sharded sort result (uint32 keys): every rank's slice ascends,
+    rank r's last key does not exceed rank r+1's first, and count and key sum of the whole
+    equal the input's."""
+    import torch
+    li = result.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    assert bool((li[1:] >= li[:-1]).all()), "a rank's slice is not sorted"
+    edge = torch.tensor([int(li[0]) if li.numel() else -1, int(li[-1]) if li.numel() else -1, li.numel(), int(li.sum())],
+                        device=result.device, dtype=torch.int64)
+    edges = [torch.zeros_like(edge) for _ in range(dist.get_world_size())]
+    dist.all_gather(edges, edge)
+    last = -1
+    for e in edges:
+        first_key, last_key, count, _ = (int(x) for x in e.tolist())
+        if count:
+            assert first_key >= last, "rank order broken: a slice starts below the previous slice's last key"
+            last = last_key
+    assert sum(int(e[2]) for e in edges) == n_in, "keys were lost or duplicated"
+    assert sum(int(e[3]) for e in edges) == checksum_in, "key checksum differs from the input's"
+
+
+def check_small_sorts_against_oracle(sharded, rank: int, world: int, dist) -> None:
+    """One untimed SortKeys (uniform uint32) and one SortPairs (Zipf uint64 keys, payload =
+    global index) of 2^20 elements in total, gathered and compared bit for bit, payload
+    included, with the CPU oracle (rank 0 compares; the oracle is the checker only)."""
+    import numpy as np
+    import torch
+    import ilgpu_b200 as ib
+    from ilgpu_b200 import synthetic
+    total = 1 << 20
+    n = total // world
+    keys = synthetic.uniform_uint32_device(n, 11, "cuda", start=rank * n)
+    out, _ = sharded.SortKeys(keys, ib.RadixSortOperations.AscendingUInt32)
+    got = _gather_variable(out.view(torch.int32), dist)
+    pk = synthetic.zipf_uint64_device(n, 12, "cuda", start=rank * n)
+    pv = (torch.arange(n, dtype=torch.int32, device="cuda") + rank * n).view(torch.uint32)
+    ok, ov = sharded.SortPairs(pk, pv, ib.RadixSortOperations.AscendingUInt64)
+    gk = _gather_variable(ok.view(torch.int64), dist)
+    gv = _gather_variable(ov.view(torch.int32), dist)
+    if rank == 0:
+        from oracle import cpu_oracle as oracle
+        expect, _ = oracle.radix_sort(synthetic.uniform_uint32(world * n, 11))
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), expect), "sharded SortKeys differs from the oracle"
+        ek, ev = oracle.radix_sort(synthetic.zipf_uint64(world * n, 12), np.arange(world * n, dtype=np.uint32))
+        assert np.array_equal(gk.cpu().numpy().view(np.uint64), ek), "sharded SortPairs keys differ from the oracle"
+        assert np.array_equal(gv.cpu().numpy().view(np.uint32), ev), "sharded SortPairs payload differs from the oracle"
 
 
 def run_profile_case(case: str) -> None:
@@ -354,7 +460,7 @@ def run_native(args) -> None:
     # One fresh unsorted buffer per step (the sort is in place); 256 MiB each, larger than L2.
     nbuf = steps + warmup
     pristine = synthetic.uniform_uint32_device(n, SEED, "cuda", start=rank * n)
-    checksum_in = int(pristine.view(torch.int32).to(torch.int64).sum().item())
+    checksum_in = int((pristine.view(torch.int32).to(torch.int64) & 0xFFFFFFFF).sum().item())
 
     if world == 1:
         bufs = [pristine.clone() for _ in range(nbuf)]
@@ -401,20 +507,28 @@ def run_native(args) -> None:
     ms_per_step = ms_total / steps
     value = world * n / (ms_per_step * 1e-3) / 1e9
 
-    # sanity of the timed work (the parity tests proper live in tests/)
+    # checks of the timed work, outside the timed region (the parity tests proper live in tests/)
     final = result_of(warmup + steps - 1)
-    li = final.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
-    assert bool((li[1:] >= li[:-1]).all()), "result is not sorted"
     if world == 1:
-        assert int(final.view(torch.int32).to(torch.int64).sum().item()) == checksum_in, "keys were lost"
-    del li, final
+        li = final.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+        assert bool((li[1:] >= li[:-1]).all()), "result is not sorted"
+        assert int(li.sum().item()) == checksum_in, "keys were lost"
+        del li
+    else:
+        t = torch.tensor([checksum_in], device="cuda", dtype=torch.int64)
+        dist.all_reduce(t)
+        check_sharded_sort(final, int(t.item()), world * n, dist)
+        check_small_sorts_against_oracle(sharded, rank, world, dist)
+    parity_checked = True
+    del final
 
     # end to end through the public API with host buffers: H2D of the keys, sort, D2H of the result
     e2e_steps = max(1, min(steps, 8))
     host_in = torch.empty(n, dtype=torch.uint32).pin_memory()
     host_in.copy_(pristine.cpu())
-    host_out = torch.empty(n, dtype=torch.uint32).pin_memory()
+    host_out = torch.empty(n if world == 1 else 2 * n, dtype=torch.uint32).pin_memory()
     dev = bufs[0]
+    d2h_bytes = [4 * n]
 
     def e2e_fn(i):
         dev.copy_(host_in, non_blocking=True)
@@ -423,7 +537,9 @@ def run_native(args) -> None:
             host_out.copy_(dev, non_blocking=True)
         else:
             out, count = sharded.SortKeys(dev, op)
-            host_out[: min(n, out.numel())].copy_(out[: min(n, out.numel())], non_blocking=True)
+            count = min(count, host_out.numel())
+            host_out[:count].copy_(out[:count], non_blocking=True)     # this rank's slice of the result
+            d2h_bytes[0] = 4 * count
     for i in range(2):
         e2e_fn(i)
     torch.cuda.synchronize()
@@ -522,10 +638,11 @@ def run_native(args) -> None:
                 "how": "live time of the sort call x the passes' share of it in the ncu launch list, / 4 passes",
             }),
         },
-        "e2e": {"value": e2e_value, "unit": "Gkeys/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4 * n,
+        "e2e": {"value": e2e_value, "unit": "Gkeys/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": d2h_bytes[0],
                 "ms_per_step": e2e_ms, "ms_per_step_serial": e2e_serial_ms, "how": e2e_note},
         "gpu_launches": launches_per_step * steps,
         "clocks": clocks,
+        "parity_checked": parity_checked,
     }
     if secondary is not None:
         line["secondary"] = secondary

@@ -18,11 +18,14 @@ from .algorithms import (
     ScanKind,
     ScanProvider,
     ScanReduceOperations,
+    Sequencer,
+    Sequencers,
 )
 
 __all__ = [
     "Accelerator", "ArgumentNullException", "ArgumentOutOfRangeException", "B200AlgException",
     "EqualWidthClampLocator", "InvalidOperationException", "ModuloLocator", "NotSupportedException",
     "RadixSortOperations", "RadixSortProvider", "ScanKind", "ScanProvider", "ScanReduceOperations",
+    "Sequencer", "Sequencers",
     "_native",
 ]

@@ -32,6 +32,7 @@ SIGNATURES = {
     "b200alg_radix_sort_temp_bytes": (_int, [_int, _i64, _int, ctypes.POINTER(_i64)]),
     "b200alg_radix_sort_keys": (_int, [_vp, _vp, _i64, _i64, _int, _int, _vp, _i64]),
     "b200alg_radix_sort_pairs": (_int, [_vp, _vp, _vp, _i64, _int, _int, _int, _vp, _i64]),
+    "b200alg_radix_sort_pairs_sequence": (_int, [_vp, _vp, _vp, _i64, _int, _int, _int, _vp, _i64]),
     "b200alg_bucket_partition_temp_bytes": (_int, [_int, _i64, ctypes.POINTER(_i64)]),
     "b200alg_bucket_partition": (_int, [_vp, _vp, _vp, _i64, _int, _int, _int, _vp, _vp, _int, _i64, _vp, _vp, _vp, _vp, _i64]),
     "b200alg_bucket_count": (_int, [_vp, _vp, _i64, _int, _int, _vp, _vp, _int, _i64, _vp, _vp, _i64]),

@@ -133,6 +133,25 @@ for _tn, _td in _TYPE_NAMES.items():
     setattr(RadixSortOperations, "Descending" + _tn, RadixSortOperation("Descending" + _tn, _td, True))
 
 
+@dataclass(frozen=True)
+class Sequencer:
+    """ISequencer<T> restricted to the reference's built-in, stateless sequencers
+    (Sequencer.cs:37-72, Sequencers.tt:26-38): element i is the index converted to T."""
+    name: str
+    dtype: torch.dtype
+
+
+class Sequencers:
+    IndexSequencer = Sequencer("IndexSequencer", torch.int32)
+    HalfSequencer = Sequencer("HalfSequencer", torch.float16)
+    FloatSequencer = Sequencer("FloatSequencer", torch.float32)
+    DoubleSequencer = Sequencer("DoubleSequencer", torch.float64)
+
+
+for _tn in ("Int8", "UInt8", "Int16", "UInt16", "Int32", "UInt32", "Int64", "UInt64"):
+    setattr(Sequencers, _tn + "Sequencer", Sequencer(_tn + "Sequencer", _TYPE_NAMES[_tn]))
+
+
 class ScanKind(enum.Enum):
     """ScanExtensions.cs:27-38."""
     Inclusive = 0
@@ -305,11 +324,36 @@ class Accelerator:
 
         return sort
 
-    def CreateRadixSortPairs(self, operation: RadixSortOperation, float_total_order: bool = False):
+    def CreateRadixSortPairs(self, operation: RadixSortOperation, float_total_order: bool = False,
+                             sequencer: type | None = None):
         """Returns ``sort(stream, keys, values, temp)`` (RadixSortPairs delegate,
-        RadixSortExtensions.cs:54-108); keys and values are reordered together, stably."""
+        RadixSortExtensions.cs:54-108); keys and values are reordered together, stably.
+        With ``sequencer=Sequencers`` the sequencer overload (:1017-1074) is returned instead:
+        ``sort(stream, keys, values, sequencer, temp)``, where the values entering the sort
+        are ``sequencer.ComputeSequenceElement(i)`` and ``values`` only receives the result."""
         code = dtype_code(operation.dtype)
         order = (N.SORT_DESCENDING if operation.descending else 0) | (N.SORT_FLOAT_TOTAL_ORDER if float_total_order else 0)
+
+        def sort_sequenced(stream, keys, values, seq, temp):
+            if not isinstance(seq, Sequencer):
+                raise NotSupportedException("only the built-in sequencers cross the native boundary")
+            _check_view(keys, "keys", operation.dtype)
+            _check_view(values, "values", seq.dtype)
+            n = keys.numel()
+            if n > 2**31 - 1:
+                raise NotSupportedException("NotSupportedArrayView64")
+            if values.numel() != n:
+                raise ArgumentOutOfRangeException("values")
+            if _stride(keys) != 1 or _stride(values) != 1:
+                raise NotSupportedException("pairs are sorted from dense views")
+            _check_temp(temp, self.ComputeRadixSortPairsTempStorageSize(operation, values.dtype, n))
+            with self.Bind():
+                B200AlgException.ThrowIfFailed(self.L.b200alg_radix_sort_pairs_sequence(
+                    _stream_ptr(stream), _ptr(keys), _ptr(values), n, code, dtype_code(seq.dtype), order,
+                    _ptr(temp), temp.numel() * 4))
+
+        if sequencer is not None:
+            return sort_sequenced
 
         def sort(stream, keys, values, temp):
             _check_view(keys, "keys", operation.dtype)

@@ -6,6 +6,7 @@
 #include <stdint.h>
 #include <float.h>
 #include <limits.h>
+#include <mutex>
 
 #include "../../include/b200alg.h"
 
@@ -27,8 +28,45 @@ inline int cuda_fail(cudaError_t e) {
 
 #define B200ALG_LAUNCH_CHECK() B200ALG_CUDA_TRY(cudaGetLastError())
 
-// Number of SMs of the current device (148 on B200); cached per device ordinal.
+// Number of SMs of the current device (148 on B200).
 int sm_count();
+
+// The CUDA context that is current on the calling thread, as an opaque handle (NULL when
+// the driver cannot be asked).  A host such as ILGPU creates a context of its own per
+// accelerator, so everything that CUDA keeps per context (function attributes, addresses of
+// __device__ symbols) is cached by this handle, never by device ordinal.
+void *current_context();
+
+// Device address, in the current context, of the built-in scratch array of b200alg_scan_static.
+int static_scan_scratch(void **out);
+
+// A value per CUDA context, filled in on first use; safe for concurrent host threads.  A
+// handful of contexts is the expected load, so the lookup is a linear scan under a mutex.
+template <typename T> class ContextCache {
+public:
+    bool find(T *out) {
+        void *ctx = current_context();
+        if (!ctx) return false;
+        std::lock_guard<std::mutex> g(mu_);
+        for (int i = 0; i < used_; ++i)
+            if (ctx_[i] == ctx) { *out = val_[i]; return true; }
+        return false;
+    }
+    void store(const T &v) {
+        void *ctx = current_context();
+        if (!ctx) return;
+        std::lock_guard<std::mutex> g(mu_);
+        for (int i = 0; i < used_; ++i)
+            if (ctx_[i] == ctx) { val_[i] = v; return; }
+        if (used_ < kSlots) { ctx_[used_] = ctx; val_[used_] = v; ++used_; }
+    }
+private:
+    static constexpr int kSlots = 64;
+    std::mutex mu_;
+    void *ctx_[kSlots] = {};
+    T val_[kSlots] = {};
+    int used_ = 0;
+};
 
 inline int dtype_bytes(int dt) {
     switch (dt) {
@@ -44,6 +82,11 @@ inline bool is_atomic_numeric(int dt) {
     return dt == B200ALG_I32 || dt == B200ALG_U32 || dt == B200ALG_I64 || dt == B200ALG_U64 ||
            dt == B200ALG_F32 || dt == B200ALG_F64;
 }
+
+// Longest view an entry point accepts.  The reference stops at int.MaxValue elements
+// (ErrorMessages.NotSupportedArrayView64); that check stays with the host-side mirror, the
+// kernels index with 64 bits.
+constexpr int64_t kMaxElements = 1ll << 38;  // per-block 32-bit counters of the histogram kernels hold up to here
 
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -136,6 +179,66 @@ __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int *p) {
     unsigned int v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+
+// ---- bulk asynchronous copies (TMA) completing on an mbarrier -----------------------------
+// Upper bound on polls of an mbarrier before a kernel gives up waiting for a bulk copy.
+constexpr unsigned int kMaxBarrierPolls = 1u << 22;
+
+__device__ __forceinline__ unsigned int smem_addr(const void *p) { return (unsigned int)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned int parity) {
+    unsigned int ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bulk copy global -> this block's shared memory (no multicast); both addresses and the size
+// are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, unsigned int bytes, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned int parity) {
+    for (unsigned int polls = 0; polls < kMaxBarrierPolls; ++polls)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A kernel launched with launch_dependent() may start while the kernel before it on the
+// stream still runs; it must call grid_dependency_wait() before it touches anything that
+// kernel writes (the wait returns once the earlier kernel has completed and its writes are
+// visible).  The earlier kernel calls grid_dependency_release() to let the next one start.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
 }
 
 #endif  // __CUDACC__

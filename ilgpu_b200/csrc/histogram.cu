@@ -250,7 +250,7 @@ extern "C" int b200alg_histogram(void *stream, const void *in, int64_t stride, i
     if (!in || !bins) return B200ALG_INVALID_ARGUMENT;
     if (n < 0 || stride < 1 || num_bins < 1) return B200ALG_INVALID_ARGUMENT;
     if (!is_atomic_numeric(in_dtype) || !is_atomic_numeric(bin_dtype)) return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX || num_bins > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements || num_bins > INT32_MAX) return B200ALG_TOO_LARGE;
     if (locator == B200ALG_LOCATOR_EQUAL_WIDTH_CLAMP && !(hi > lo)) return B200ALG_INVALID_ARGUMENT;
     if (((uintptr_t)in % dtype_bytes(in_dtype)) || ((uintptr_t)bins % dtype_bytes(bin_dtype)) ||
         (overflow && ((uintptr_t)overflow % 4)))

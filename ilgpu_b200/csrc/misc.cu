@@ -6,16 +6,33 @@ namespace b200alg {
 
 thread_local int g_last_cuda_error = 0;
 
+void *current_context() {
+    // cuCtxGetCurrent through the runtime's table of driver entry points: no link-time
+    // dependency on the driver library.
+    typedef int (*GetCurrentFn)(void **);
+    static GetCurrentFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (GetCurrentFn)p;
+    }();
+    void *ctx = nullptr;
+    if (!fn || fn(&ctx) != 0) return nullptr;
+    return ctx;  // NULL until the first runtime call of the thread has bound a context
+}
+
 int sm_count() {
-    static int cached[64] = {0};
+    static ContextCache<int> cache;
+    int v = 0;
+    if (cache.find(&v)) return v;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int v = 0;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
-        cached[dev] = v;
-    }
-    return cached[dev];
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+        return 148;
+    cache.store(v);
+    return v;
 }
 
 template <typename T>
@@ -29,6 +46,19 @@ __global__ void __launch_bounds__(256) sequence_kernel(T *view, int64_t n, T sta
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step)
         view[i] = (T)(start + (T)i * step_value);
+}
+
+// Test-only: one warp polls a word that nothing ever sets, with the same bounded-wait pattern
+// as the look-back loops of the product kernels, and records that it gave up.
+__global__ void wait_probe_kernel(TempHeader *hdr, const unsigned int *word, unsigned int max_polls) {
+    unsigned int polls = 0;
+    while (ld_acquire_u32(word) == 0u) {
+        if (++polls > max_polls) {
+            atomicExch(&hdr->wait_limit_hit, 1u);
+            break;
+        }
+        __nanosleep(20);
+    }
 }
 
 static int grid_for(int64_t n) {
@@ -52,7 +82,7 @@ extern "C" const char *b200alg_status_string(int status) {
     case B200ALG_CUDA_ERROR: return "CUDA error (see b200alg_last_cuda_error)";
     case B200ALG_WAIT_LIMIT: return "a device-side wait exceeded its iteration limit";
     case B200ALG_MISALIGNED: return "pointer not aligned";
-    case B200ALG_TOO_LARGE: return "more than INT32_MAX elements";
+    case B200ALG_TOO_LARGE: return "more elements than the library indexes (2^38)";
     case B200ALG_STATIC_LIMIT: return "more elements than the built-in scratch of this entry point covers";
     }
     return "unknown status";
@@ -62,6 +92,7 @@ extern "C" int b200alg_last_cuda_error(void) { return g_last_cuda_error; }
 
 extern "C" int b200alg_initialize(void *stream, void *view, int64_t stride, int64_t n, int elem_bytes, const void *value) {
     if (n < 0 || stride < 1 || (n > 0 && !view) || !value) return B200ALG_INVALID_ARGUMENT;
+    if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8 && elem_bytes != 16) return B200ALG_UNSUPPORTED;
     if (n == 0) return B200ALG_OK;
     if ((uintptr_t)view % elem_bytes) return B200ALG_MISALIGNED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -96,8 +127,23 @@ extern "C" int b200alg_sequence(void *stream, void *view, int64_t n, int dtype, 
     return B200ALG_OK;
 }
 
+extern "C" int b200alg_testing_wait_limit(void *stream, void *temp, int64_t temp_bytes, unsigned int max_polls) {
+    if (!temp || temp_bytes < 512 || ((uintptr_t)temp % 256)) return B200ALG_INVALID_ARGUMENT;
+    if (max_polls > 1000000u) return B200ALG_INVALID_ARGUMENT;  // a test never waits long
+    cudaStream_t s = (cudaStream_t)stream;
+    B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, 512, s));
+    wait_probe_kernel<<<1, 32, 0, s>>>((TempHeader *)temp, (const unsigned int *)((const char *)temp + 256), max_polls);
+    B200ALG_LAUNCH_CHECK();
+    return B200ALG_OK;
+}
+
 extern "C" int b200alg_device_status(void *stream, const void *temp) {
-    if (!temp) return B200ALG_INVALID_ARGUMENT;
+    if (!temp) {  // the built-in scratch array of b200alg_scan_static
+        void *scratch = nullptr;
+        const int rc = static_scan_scratch(&scratch);
+        if (rc != B200ALG_OK) return rc;
+        temp = scratch;
+    }
     unsigned int flag = 0;
     cudaStream_t s = (cudaStream_t)stream;
     B200ALG_CUDA_TRY(cudaMemcpyAsync(&flag, temp, sizeof(flag), cudaMemcpyDeviceToHost, s));

@@ -24,11 +24,35 @@ constexpr int kMaxPasses = 8;
 
 // Control words that live in TempHeader::reserved.
 enum : int {
-    kCtlTicket = 0,        // [0..7]  reserved (tiles are assigned round-robin, no tickets)
+    kCtlTicket = 0,        // [0..7]  next tile of each pass (tiles are handed out in order)
     kCtlSkip = 8,          // [8..15] 1 = every key has the same digit at this position
     kCtlSrcIsAlt = 16,     // [16..23] 1 = this pass reads the alternate buffer
-    kCtlFinalInAlt = 24    // 1 = the sorted data ended in the alternate buffer
+    kCtlFinalInAlt = 24,   // 1 = the sorted data ended in the alternate buffer
+    kCtlFirstPass = 25     // first pass that runs (kNoPass when every pass is skipped)
 };
+constexpr unsigned int kNoPass = 0xFFu;
+
+// Values that are a function of the element's index (the reference's sequencers:
+// IndexSequencer and the integer / Half / Float / Double sequencers, Sequencer.cs:37-72,
+// Sequencers.tt:26-38): the pairs sort can produce them in its first pass instead of reading
+// a value view.
+enum : int { kSeqNone = 0, kSeqInteger = 1, kSeqFloating = 2 };
+template <typename V> __device__ __forceinline__ V sequence_value(int kind, int64_t i) {
+    if constexpr (sizeof(V) == 2) {
+        if (kind == kSeqFloating) return (V)__half_as_ushort(__float2half_rn((float)i));
+        return (V)i;
+    } else if constexpr (sizeof(V) == 4) {
+        if (kind == kSeqFloating) return (V)__float_as_uint((float)i);
+        return (V)i;
+    } else if constexpr (sizeof(V) == 8) {
+        if (kind == kSeqFloating) return (V)__double_as_longlong((double)i);
+        return (V)i;
+    } else if constexpr (sizeof(V) == 1) {
+        return (V)i;
+    } else {
+        return V{};
+    }
+}
 
 // Key transform: bits = raw ^ (sign(raw) ? xor_neg : xor_pos) covers every key type of
 // RadixSortOperations.tt:77-93 and the descending complement of :122-123.
@@ -75,7 +99,7 @@ constexpr int kHistoMaxSmem = 128 * 1024;
 
 template <typename K, int RSHIFT>
 __global__ void __launch_bounds__(kHistoThreads)
-sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, KeyXform<K> xf, unsigned int *ghist) {
+sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, KeyXform<K> xf, unsigned long long *ghist) {
     constexpr int P = sizeof(K);
     constexpr int rshift = RSHIFT;
     // replicas are interleaved ([position][digit][replica]) so that the lanes of a warp spread
@@ -128,31 +152,32 @@ sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, Key
     for (int i = threadIdx.x; i < P * kRadix; i += kHistoThreads) {
         unsigned int c = 0;
         for (int r = 0; r < replicas; ++r) c += sh[(i << rshift) + ((r + threadIdx.x) & (replicas - 1))];
-        if (c) atomicAdd(ghist + i, c);
+        if (c) atomicAdd(ghist + i, (unsigned long long)c);
     }
 }
 
 // ---- 2. global digit offsets, skipped passes, buffer schedule ---------------------------
 __global__ void __launch_bounds__(kRadix)
-sort_offsets_kernel(const unsigned int *ghist, unsigned int *gbase, TempHeader *hdr, int passes, unsigned int n) {
-    __shared__ unsigned int warp_sum[kRadix / 32];
+sort_offsets_kernel(const unsigned long long *ghist, unsigned long long *gbase, TempHeader *hdr, int passes, unsigned long long n) {
+    __shared__ unsigned long long warp_sum[kRadix / 32];
     __shared__ int s_skip;
     const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
     int src_is_alt = 0;
+    unsigned int first = kNoPass;
     for (int p = 0; p < passes; ++p) {
         if (d == 0) s_skip = 0;
         __syncthreads();
-        const unsigned int c = ghist[p * kRadix + d];
+        const unsigned long long c = ghist[p * kRadix + d];
         if (c == n) s_skip = 1;
-        unsigned int incl = c;
+        unsigned long long incl = c;
 #pragma unroll
         for (int k = 1; k < 32; k <<= 1) {
-            unsigned int up = __shfl_up_sync(0xffffffffu, incl, k);
+            unsigned long long up = __shfl_up_sync(0xffffffffu, incl, k);
             if (lane >= k) incl += up;
         }
         if (lane == 31) warp_sum[warp] = incl;
         __syncthreads();
-        unsigned int before = 0;
+        unsigned long long before = 0;
         for (int w = 0; w < warp; ++w) before += warp_sum[w];
         gbase[p * kRadix + d] = before + incl - c;
         const int skip = s_skip;
@@ -160,10 +185,14 @@ sort_offsets_kernel(const unsigned int *ghist, unsigned int *gbase, TempHeader *
             hdr->reserved[kCtlSkip + p] = (unsigned)skip;
             hdr->reserved[kCtlSrcIsAlt + p] = (unsigned)src_is_alt;
         }
+        if (!skip && d == 0 && first == kNoPass) first = (unsigned)p;
         if (!skip) src_is_alt ^= 1;
         __syncthreads();
     }
-    if (d == 0) hdr->reserved[kCtlFinalInAlt] = (unsigned)src_is_alt;
+    if (d == 0) {
+        hdr->reserved[kCtlFinalInAlt] = (unsigned)src_is_alt;
+        hdr->reserved[kCtlFirstPass] = first;
+    }
 }
 
 // ---- 3. one digit pass -------------------------------------------------------------------
@@ -243,54 +272,39 @@ struct NoValue {};
 template <typename V> struct ValueBytes { static constexpr int value = sizeof(V); };
 template <> struct ValueBytes<NoValue> { static constexpr int value = 0; };
 
-#ifndef B200ALG_RANK_GROUP
-#define B200ALG_RANK_GROUP 1
-#endif
-constexpr int kRankGroup = B200ALG_RANK_GROUP;  // items ranked together, each with a mask table of its own (1, 2 or 4)
+// Index of an element of the whole view: 32 bits while the look-back words are, else 64.
+template <typename SW> struct IndexOf { using type = unsigned int; };
+template <> struct IndexOf<unsigned long long> { using type = unsigned long long; };
+
+// Full dense tiles are staged in shared memory by one bulk asynchronous copy (TMA, no
+// multicast) that is issued a tile ahead.
+constexpr bool kSortTma = true;
+constexpr int kLookWindow = 4;  // predecessors examined per look-back round
 
 template <typename K, typename V, bool KEEP_DIGITS, int THREADS, int ITEMS>
 struct OnesweepSmem {
     static constexpr int TILE = THREADS * ITEMS;
+    static constexpr int WARPS = THREADS / 32;
     static constexpr int VB = ValueBytes<V>::value;
-    // keys and values are staged side by side when that stays small enough for two blocks per
-    // SM; otherwise the values reuse the keys' staging buffer in a second round
+    // keys and values are reordered side by side when that stays small enough for two blocks
+    // per SM; otherwise the values reuse the keys' buffer in a second round
     static constexpr bool SPLIT = VB != 0 && (size_t)TILE * ((int)sizeof(K) + VB) <= 72 * 1024;
-    static constexpr int STAGE = SPLIT ? (int)sizeof(K) + VB : ((int)sizeof(K) > VB ? (int)sizeof(K) : VB);
-    static constexpr size_t base_bytes = (size_t)TILE * STAGE + (size_t)(THREADS / 32) * kRadix * 8 + kRadix * 4 * 2 + 64 +
-                                         (KEEP_DIGITS ? (size_t)TILE + kRadix * 16 : 0);
-    // mask tables: #0 beside the counts, #1 after everything else, #2 and #3 in the staging
-    // buffer, which is idle while a tile is ranked
-    static constexpr size_t mask_bytes = (size_t)(THREADS / 32) * kRadix * 4;
-    static constexpr size_t bytes = base_bytes + (kRankGroup >= 2 ? mask_bytes : 0);
-    static_assert(kRankGroup <= 2 || (size_t)TILE * STAGE >= (kRankGroup - 2) * mask_bytes, "staging too small for the mask tables");
+    static constexpr int SLOT = SPLIT ? (int)sizeof(K) + VB : ((int)sizeof(K) > VB ? (int)sizeof(K) : VB);
+    // [sorted: the reorder buffer][counts per warp and digit][lane masks per warp and digit]
+    // [digit's first slot in the tile, digit's count][digit's global offset][small words +
+    // mbarrier][pass description][digit of every slot][splitters][staged keys]
+    static constexpr size_t off_sorted = 0;
+    static constexpr size_t off_count = (size_t)TILE * SLOT;
+    static constexpr size_t off_mask = off_count + (size_t)WARPS * kRadix * 4;
+    static constexpr size_t off_excl = off_mask + (size_t)WARPS * kRadix * 4;
+    static constexpr size_t off_goff = off_excl + kRadix * 8;
+    static constexpr size_t off_misc = off_goff + kRadix * 8;
+    static constexpr size_t off_context = off_misc + 128;   // the block's PassContext
+    static constexpr size_t off_digits = off_context + 128;
+    static constexpr size_t off_splitters = off_digits + (KEEP_DIGITS ? (size_t)TILE : 0);
+    static constexpr size_t off_stage = (off_splitters + (KEEP_DIGITS ? (size_t)kRadix * 16 : 0) + 127) / 128 * 128;
+    static constexpr size_t bytes = off_stage + (kSortTma ? (size_t)TILE * sizeof(K) : 0);
 };
-
-#ifndef B200ALG_LOOK_WINDOW
-#define B200ALG_LOOK_WINDOW 4
-#endif
-
-#ifdef B200ALG_EXP_TIMING
-// Experimental builds only: thread 0 of every tile records the global timer at phase borders.
-__device__ unsigned long long *g_exp_debug = nullptr;
-#define B200ALG_STAMP(k)                                                  \
-    do {                                                                  \
-        if (threadIdx.x == 0) {                                           \
-            unsigned long long *dbg = g_exp_debug;                        \
-            unsigned long long t;                                         \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));         \
-            if (dbg) dbg[(size_t)tile * 16 + (k)] = t;                    \
-        }                                                                 \
-    } while (0)
-#define B200ALG_RECORD(k, v)                                              \
-    do {                                                                  \
-        if (threadIdx.x == 0 && g_exp_debug) g_exp_debug[(size_t)tile * 16 + (k)] = (v); \
-    } while (0)
-#define B200ALG_ONESWEEP_MIN_BLOCKS 2
-#else
-#define B200ALG_STAMP(k) do {} while (0)
-#define B200ALG_RECORD(k, v) do {} while (0)
-#define B200ALG_ONESWEEP_MIN_BLOCKS 2
-#endif
 
 // Everything one block needs to know about the pass it works on.
 template <typename K, typename V, typename SW> struct PassContext {
@@ -301,20 +315,76 @@ template <typename K, typename V, typename SW> struct PassContext {
     V *vdst;
     int64_t n;
     int num_tiles;
-    bool dense;
+    bool dense;   // the source is contiguous
+    bool bulk;    // full tiles of the source can be staged by bulk copies (dense, 16-byte aligned)
+    int value_seq;  // not kSeqNone: this pass makes the values from the element index instead of reading them
     TempHeader *hdr;
-    const unsigned int *gbase;
+    unsigned int *ticket;
+    const unsigned long long *gbase;
     SW *status, *status_next;
 };
 
-// Keys of one tile in warp-striped order: item i of lane l is element
-// warp * 32 * ITEMS + i * 32 + l of the tile.
-template <typename K, typename V, typename SW, int THREADS, int ITEMS>
-__device__ __forceinline__ void load_tile_keys(K (&key)[ITEMS], const PassContext<K, V, SW> &c, int tile) {
+// Hands out the block's next tile and, when that tile is a full one of a bulk-copyable
+// source, starts the copy of its keys into the staging buffer.  One thread calls this once
+// every thread of the block has taken the current tile's keys out of the staging buffer.
+template <typename K, typename V, typename SW, int TILE>
+__device__ __forceinline__ int take_ticket(const PassContext<K, V, SW> &c, K *stage, unsigned long long *bar) {
+    const int next = (int)atomicAdd(c.ticket, 1u);
+    if (kSortTma && c.bulk && next < c.num_tiles && (int64_t)(next + 1) * TILE <= c.n) {
+        mbar_expect_tx(bar, (unsigned int)(TILE * sizeof(K)));
+        bulk_load(stage, c.src + (int64_t)next * TILE, (unsigned int)(TILE * sizeof(K)), bar);
+    }
+    return next;
+}
+
+// One tile of one digit pass; returns the block's next tile.  FAST = the tile is full and both
+// buffers are dense (no bounds checks, no stride arithmetic).  Keys are held in warp-striped
+// order: item i of lane l is element warp * 32 * ITEMS + i * 32 + l of the tile.
+template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS, bool FAST>
+__device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int tile, unsigned int &bulk_phase,
+                                             const Digit &dg, unsigned char *smem_raw) {
+    constexpr int WARPS = THREADS / 32;
     constexpr int TILE = THREADS * ITEMS;
-    const int warp_base = (threadIdx.x >> 5) * 32 * ITEMS + (threadIdx.x & 31);
+    constexpr bool HAS_VALUES = ValueBytes<V>::value != 0;
+    using S = StatusWord<SW>;
+    using Idx = typename IndexOf<SW>::type;
+    using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
+    K *skeys = reinterpret_cast<K *>(smem_raw + L::off_sorted);
+    V *svals = reinterpret_cast<V *>(smem_raw + L::off_sorted + (L::SPLIT ? (size_t)TILE * sizeof(K) : 0));
+    // count_tbl[w][d]: number, later first slot, of the d-keys of warp w; mask_tbl[w][d]: lanes of
+    // warp w that hold d in the item being ranked (zero between items)
+    unsigned int *count_tbl = reinterpret_cast<unsigned int *>(smem_raw + L::off_count);
+    unsigned int *mask_tbl = reinterpret_cast<unsigned int *>(smem_raw + L::off_mask);
+    unsigned int *bin_excl = reinterpret_cast<unsigned int *>(smem_raw + L::off_excl);  // digit's first slot inside the tile
+    unsigned int *bin_count = bin_excl + kRadix;                                         // digit's keys in the tile
+    Idx *bin_goff = reinterpret_cast<Idx *>(smem_raw + L::off_goff);  // global index of slot p is bin_goff[d] + p
+    unsigned int *misc = reinterpret_cast<unsigned int *>(smem_raw + L::off_misc);  // [0..7] sums of the digit warps, [8] next tile
+    unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + L::off_misc + 64);
+    unsigned char *sdigit = smem_raw + L::off_digits;  // only when digits need the index
+    K *stage = reinterpret_cast<K *>(smem_raw + L::off_stage);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t tile_base = (int64_t)tile * TILE;
-    if (c.dense && tile_base + TILE <= c.n) {
+    const int valid = FAST ? TILE : (int)((c.n - tile_base) < TILE ? (c.n - tile_base) : TILE);
+    const int warp_base = warp * 32 * ITEMS + lane;
+    unsigned int *my_count = count_tbl + warp * kRadix;
+    unsigned int *my_mask = mask_tbl + warp * kRadix;
+
+    // The warp's own row of the count table starts at zero (nobody else touches it before the
+    // first block-wide barrier of the tile); its lane masks are left at zero by every item.
+    {
+        uint4 *zc = reinterpret_cast<uint4 *>(my_count);
+#pragma unroll
+        for (int i = 0; i < kRadix / 4 / 32; ++i) zc[i * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
+    }
+
+    K key[ITEMS];
+    if (FAST && kSortTma && c.bulk) {
+        if (!mbar_wait(bar, bulk_phase) && lane == 0) atomicExch(&c.hdr->wait_limit_hit, 1u);
+        bulk_phase ^= 1u;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) key[i] = stage[warp_base + i * 32];
+    } else if (FAST) {
         const K *p = c.src + tile_base + warp_base;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) key[i] = p[i * 32];
@@ -325,129 +395,76 @@ __device__ __forceinline__ void load_tile_keys(K (&key)[ITEMS], const PassContex
             key[i] = idx < c.n ? c.src[idx * c.src_stride] : K(0);
         }
     }
-}
-
-// One tile of one digit pass; `key` holds the tile's keys on entry and the keys of
-// `next_tile` (if there is one) on return: they are requested as soon as this tile's keys
-// have moved to shared memory, so the loads are in flight during the look-back and the
-// write-out.  FAST = the tile is full and both buffers are dense (no bounds checks, no
-// stride arithmetic).
-template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS, bool FAST>
-__device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext<K, V, SW> &c, int tile, int next_tile,
-                                              const Digit &dg, unsigned char *smem_raw) {
-    constexpr int WARPS = THREADS / 32;
-    constexpr int TILE = THREADS * ITEMS;
-    constexpr bool HAS_VALUES = ValueBytes<V>::value != 0;
-    constexpr int kLookWindow = B200ALG_LOOK_WINDOW;  // predecessors examined per look-back round
-    using S = StatusWord<SW>;
-    using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
-    K *skeys = reinterpret_cast<K *>(smem_raw);
-    // warp_tbl[w][d]: count, later offset, of digit d in warp w; mask_tbl[w][d]: lanes of warp w
-    // that hold d in the item being ranked (zero between items)
-    unsigned int *warp_tbl = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE);
-    unsigned int *mask_tbl = warp_tbl + WARPS * kRadix;
-    unsigned int *bin_excl = mask_tbl + WARPS * kRadix;  // digit's first slot inside the tile
-    unsigned int *bin_goff = bin_excl + kRadix;            // global index of slot p is bin_goff[d] + p
-    unsigned int *misc = bin_goff + kRadix;                // [1..8] warp sums
-    unsigned char *sdigit = reinterpret_cast<unsigned char *>(misc + 16);  // only when digits need the index
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int64_t tile_base = (int64_t)tile * TILE;
-    const int valid = FAST ? TILE : (int)((c.n - tile_base) < TILE ? (c.n - tile_base) : TILE);
-    const int warp_base = warp * 32 * ITEMS + lane;
-
-    {
-        uint4 *z = reinterpret_cast<uint4 *>(warp_tbl);
-        for (int i = tid; i < WARPS * kRadix / 4; i += THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (kRankGroup > 2) {  // the mask tables that live in the staging buffer
-            uint4 *zs = reinterpret_cast<uint4 *>(smem_raw);
-            for (int i = tid; i < (kRankGroup - 2) * WARPS * kRadix / 4; i += THREADS) zs[i] = make_uint4(0u, 0u, 0u, 0u);
+    V val[HAS_VALUES ? ITEMS : 1];
+    if constexpr (HAS_VALUES) {  // requested now, needed after the ranking
+        bool from_index = false;
+        if constexpr (sizeof(V) <= 8) from_index = c.value_seq != kSeqNone;
+        if (from_index) {
+            if constexpr (sizeof(V) <= 8) {
+#pragma unroll
+                for (int i = 0; i < ITEMS; ++i) val[i] = sequence_value<V>(c.value_seq, tile_base + warp_base + i * 32);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+                const int local = warp_base + i * 32;
+                if (FAST || local < valid) val[i] = c.vsrc[tile_base + local];
+            }
         }
     }
-    __syncthreads();
-    B200ALG_STAMP(0);
+    __syncwarp();
 
     // Ranking inside the warp: for every item, the lanes that hold the same digit have to find
     // each other.  Every lane ORs its bit into the digit's mask in the warp's table and reads
     // the mask back after a warp barrier; the lowest lane of the mask adds the number of its
     // lanes to the warp's count of that digit, clears the mask and hands the previous count to
-    // the others.  kRankGroup items go through these steps together, each with a mask table of
-    // its own, so that a group costs three trips to shared memory instead of three per item.
-    // (Finding the peers with one vote per digit bit, or with the hardware match instruction,
-    // measured slower than the table.)  After the loop the warp's table holds its digit counts.
-    V val[HAS_VALUES ? ITEMS : 1];
-    if constexpr (HAS_VALUES) {  // requested now, needed after the ranking
-#pragma unroll
-        for (int i = 0; i < ITEMS; ++i) {
-            const int local = warp_base + i * 32;
-            if (FAST || local < valid) val[i] = c.vsrc[tile_base + local];
-        }
-    }
-    V *svals = reinterpret_cast<V *>(smem_raw + (L::SPLIT ? (size_t)TILE * sizeof(K) : 0));
-
-    unsigned int *my_tbl = warp_tbl + warp * kRadix;
-    unsigned int *my_mask[kRankGroup];
-#pragma unroll
-    for (int g = 0; g < kRankGroup; ++g) {
-        unsigned int *table = g == 0   ? mask_tbl
-                              : g == 1 ? reinterpret_cast<unsigned int *>(smem_raw + L::base_bytes)
-                                       : reinterpret_cast<unsigned int *>(smem_raw) + (g - 2) * WARPS * kRadix;
-        my_mask[g] = table + warp * kRadix;
-    }
+    // the others.  (Finding the peers with one warp vote per digit bit costs no shared memory
+    // but measured slower for any share of the items, and the hardware match instruction far
+    // slower.)  After the loop the warp's table holds its digit counts.
     const unsigned int lt = lanemask_lt();
     const unsigned int my_bit = 1u << lane;
     unsigned int packed[ITEMS];  // (rank among the warp's keys of that digit) << 8 | digit
-    static_assert(ITEMS % kRankGroup == 0, "items are ranked in whole groups");
 #pragma unroll
-    for (int i0 = 0; i0 < ITEMS; i0 += kRankGroup) {
-        unsigned int d[kRankGroup], peers[kRankGroup], count[kRankGroup];
-#pragma unroll
-        for (int g = 0; g < kRankGroup; ++g) {
-            const int i = i0 + g;
-            if (FAST) {
-                d[g] = dg(key[i], tile_base + warp_base + i * 32);
-            } else {
-                const int local = warp_base + i * 32;
-                d[g] = local < valid ? dg(key[i], tile_base + local) : 0xFFu;  // padding ranks behind every real key
-            }
-            atomicOr(&my_mask[g][d[g]], my_bit);
+    for (int i = 0; i < ITEMS; ++i) {
+        unsigned int d;
+        if (FAST) {
+            d = dg(key[i], tile_base + warp_base + i * 32);
+        } else {
+            const int local = warp_base + i * 32;
+            d = local < valid ? dg(key[i], tile_base + local) : 0xFFu;  // padding ranks behind every real key
         }
+        atomicOr(&my_mask[d], my_bit);
         __syncwarp();
-#pragma unroll
-        for (int g = 0; g < kRankGroup; ++g) peers[g] = my_mask[g][d[g]];
+        const unsigned int peers = my_mask[d];
         __syncwarp();
-#pragma unroll
-        for (int g = 0; g < kRankGroup; ++g) {
-            count[g] = 0u;
-            if ((peers[g] & lt) == 0u) {  // lowest lane with this digit
-                count[g] = atomicAdd(&my_tbl[d[g]], (unsigned int)__popc(peers[g]));
-                my_mask[g][d[g]] = 0u;
-            }
-            __syncwarp();  // the counts advance item by item
+        unsigned int count = 0u;
+        if ((peers & lt) == 0u) {  // lowest lane with this digit
+            count = atomicAdd(&my_count[d], (unsigned int)__popc(peers));
+            my_mask[d] = 0u;
         }
-#pragma unroll
-        for (int g = 0; g < kRankGroup; ++g) {
-            count[g] = __shfl_sync(0xffffffffu, count[g], __ffs(peers[g]) - 1);
-            packed[i0 + g] = ((count[g] + (unsigned int)__popc(peers[g] & lt)) << 8) | d[g];
-        }
+        __syncwarp();  // the counts advance item by item
+        count = __shfl_sync(0xffffffffu, count, __ffs(peers) - 1);
+        packed[i] = ((count + (unsigned int)__popc(peers & lt)) << 8) | d;
     }
-    B200ALG_STAMP(1);
-    __syncthreads();
-    B200ALG_STAMP(2);
+    __syncthreads();  // A: the tables are complete; every thread has its keys out of the staging buffer
 
-    unsigned int tile_count = 0;
+    if (tid == THREADS - 1) misc[8] = (unsigned int)take_ticket<K, V, SW, TILE>(c, stage, bar);
+
+    // The first 256 threads (one per digit) turn the warps' digit counts into slots of the
+    // reorder buffer and publish the tile's counts for the tiles behind it.
     if (tid < kRadix) {
         c.status_next[(size_t)tile * kRadix + tid] = 0;
-        // the x field of entry [w][d] becomes the number of d-keys in the warps before w
+        // entry [w][d] becomes the number of d-keys in the warps before w
         unsigned int run = 0;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const unsigned int cnt = warp_tbl[w * kRadix + tid];
-            warp_tbl[w * kRadix + tid] = run;
+            const unsigned int cnt = count_tbl[w * kRadix + tid];
+            count_tbl[w * kRadix + tid] = run;
             run += cnt;
         }
-        tile_count = run;
+        const unsigned int tile_count = run;
         S::st(c.status + (size_t)tile * kRadix + tid, (tile == 0 ? S::kIncl : S::kAgg) | (SW)tile_count);
+        bin_count[tid] = tile_count;
         // exclusive scan of the digit counts over the 256 digit threads
         unsigned int incl = tile_count;
 #pragma unroll
@@ -455,44 +472,39 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
             unsigned int up = __shfl_up_sync(0xffffffffu, incl, k);
             if (lane >= k) incl += up;
         }
-        if (lane == 31) misc[1 + warp] = incl;
-        bin_excl[tid] = incl - tile_count;  // completed below
-    }
-    __syncthreads();
-    B200ALG_STAMP(3);
-    if (tid < kRadix) {
+        if (lane == 31) misc[warp] = incl;
+        asm volatile("bar.sync 1, %0;" ::"n"(kRadix) : "memory");  // the digit threads among themselves
         unsigned int before = 0;
 #pragma unroll
-        for (int w = 0; w < kRadix / 32; ++w) before += (w < warp) ? misc[1 + w] : 0u;
-        const unsigned int excl = bin_excl[tid] + before;
+        for (int w = 0; w < kRadix / 32; ++w) before += (w < warp) ? misc[w] : 0u;
+        const unsigned int excl = incl - tile_count + before;
         bin_excl[tid] = excl;
         // fold the digit's first slot into the per-warp offsets: one table lookup per key
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) warp_tbl[w * kRadix + tid] += excl;
+        for (int w = 0; w < WARPS; ++w) count_tbl[w * kRadix + tid] += excl;
     }
-    __syncthreads();
-    B200ALG_STAMP(4);
+    __syncthreads();  // C: every key has its slot
 
-    // Scatter through shared memory so that global writes run along digit segments.
-    unsigned int pos[ITEMS];
+    // Reorder through shared memory so that global writes run along digit segments.
+    constexpr bool SECOND_ROUND = HAS_VALUES && !L::SPLIT;  // the values follow through the same buffer
+    unsigned int pos[SECOND_ROUND ? ITEMS : 1];
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const unsigned int d = packed[i] & 0xFFu;
-        pos[i] = (packed[i] >> 8) + my_tbl[d];
-        skeys[pos[i]] = key[i];
-        if constexpr (Digit::kUsesIndex) sdigit[pos[i]] = (unsigned char)d;
-        if constexpr (L::SPLIT) svals[pos[i]] = val[i];
+        const unsigned int slot = (packed[i] >> 8) + my_count[d];
+        skeys[slot] = key[i];
+        if constexpr (Digit::kUsesIndex) sdigit[slot] = (unsigned char)d;
+        if constexpr (L::SPLIT) svals[slot] = val[i];
+        if constexpr (SECOND_ROUND) pos[i] = slot;
     }
-
-    // The registers are free again: request the next tile's keys now.
-    if (next_tile < c.num_tiles) load_tile_keys<K, V, SW, THREADS, ITEMS>(key, c, next_tile);
-    B200ALG_STAMP(5);
-
-    // Decoupled look-back, one digit per thread, kLookWindow predecessors per round (their
-    // loads are independent, so a round costs one trip to L2).
-    if (tid < kRadix) {
-        unsigned int prefix = 0;
-        unsigned long long steps = 0, polls = 0;
+    // Decoupled look-back by the last 256 threads, one digit per thread, kLookWindow
+    // predecessors per round (their loads are independent, so a round costs one trip to L2).
+    // It comes after the reorder: started earlier, beside the offset phases, it only walked
+    // further back and polled more, and the pass got slower.
+    constexpr int kWalkers = THREADS - kRadix;  // first thread of the look-back group
+    if (tid >= kWalkers) {
+        const int dgt = tid - kWalkers;
+        Idx prefix = 0;
         if (tile > 0) {
             bool gave_up = false, done = false;
             int t = tile - 1;
@@ -500,7 +512,7 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
                 SW window[kLookWindow];
 #pragma unroll
                 for (int k = 0; k < kLookWindow; ++k)
-                    window[k] = t - k >= 0 ? S::ld(c.status + (size_t)(t - k) * kRadix + tid) : (SW)S::kIncl;
+                    window[k] = t - k >= 0 ? S::ld(c.status + (size_t)(t - k) * kRadix + dgt) : (SW)S::kIncl;
 #pragma unroll
                 for (int k = 0; k < kLookWindow; ++k) {
                     if (!done) {
@@ -509,14 +521,12 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
                         while ((w & ~S::kMask) == 0) {
                             if (++spins > kMaxSpin) { gave_up = true; break; }
                             __nanosleep(20);
-                            w = S::ld(c.status + (size_t)(t - k) * kRadix + tid);
+                            w = S::ld(c.status + (size_t)(t - k) * kRadix + dgt);
                         }
-                        polls += spins;
-                        ++steps;
                         if (gave_up) {
                             done = true;
                         } else {
-                            prefix += (unsigned int)(w & S::kMask);
+                            prefix += (Idx)(w & S::kMask);
                             if (w & S::kIncl) done = true;
                         }
                     }
@@ -524,17 +534,13 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
                 t -= kLookWindow;
             }
             if (gave_up) atomicExch(&c.hdr->wait_limit_hit, 1u);
-            S::st(c.status + (size_t)tile * kRadix + tid, S::kIncl | (SW)(prefix + tile_count));
+            S::st(c.status + (size_t)tile * kRadix + dgt, S::kIncl | (SW)(prefix + bin_count[dgt]));
         }
-        B200ALG_RECORD(10, steps);
-        B200ALG_RECORD(11, polls);
-        bin_goff[tid] = c.gbase[tid] + prefix - bin_excl[tid];
+        bin_goff[dgt] = (Idx)c.gbase[dgt] + prefix - (Idx)bin_excl[dgt];
     }
-    B200ALG_STAMP(6);
-    __syncthreads();
-    B200ALG_STAMP(7);
+    __syncthreads();  // D
 
-    unsigned int out_idx[ITEMS];
+    Idx out_idx[SECOND_ROUND ? ITEMS : 1];
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const int p = tid + i * THREADS;
@@ -542,32 +548,33 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
             const K k = skeys[p];
             unsigned int d;
             if constexpr (Digit::kUsesIndex) d = sdigit[p]; else d = dg(k, 0);
-            out_idx[i] = bin_goff[d] + (unsigned int)p;
+            const Idx at = bin_goff[d] + (Idx)p;
+            if constexpr (SECOND_ROUND) out_idx[i] = at;
             bool stored = false;
             if constexpr (Digit::kUsesIndex) {
                 if (dg.bucket_keys) {  // plain stores, possibly over NVLink into a peer's receive buffer
-                    reinterpret_cast<K *>(dg.bucket_keys[d])[out_idx[i]] = k;
+                    reinterpret_cast<K *>(dg.bucket_keys[d])[at] = k;
                     stored = true;
                 }
             }
             if (!stored) {
-                if (FAST) c.dst[out_idx[i]] = k; else c.dst[(int64_t)out_idx[i] * c.dst_stride] = k;
+                if (FAST) c.dst[at] = k; else c.dst[(int64_t)at * c.dst_stride] = k;
             }
             if constexpr (L::SPLIT) {  // the value travels with its key
                 bool vstored = false;
                 if constexpr (Digit::kUsesIndex) {
                     if (dg.bucket_values) {
-                        reinterpret_cast<V *>(dg.bucket_values[d])[out_idx[i]] = svals[p];
+                        reinterpret_cast<V *>(dg.bucket_values[d])[at] = svals[p];
                         vstored = true;
                     }
                 }
-                if (!vstored) c.vdst[out_idx[i]] = svals[p];
+                if (!vstored) c.vdst[at] = svals[p];
             }
         }
     }
 
-    if constexpr (HAS_VALUES && !L::SPLIT) {
-        __syncthreads();  // every key has left the staging buffer
+    if constexpr (SECOND_ROUND) {
+        __syncthreads();  // every key has left the reorder buffer
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
             const int local = warp_base + i * 32;
@@ -589,77 +596,85 @@ __device__ __forceinline__ void onesweep_tile(K (&key)[ITEMS], const PassContext
             }
         }
     }
-    B200ALG_STAMP(8);
-    __syncthreads();  // staging buffer and tables are reused by the block's next tile
-    B200ALG_STAMP(9);
+    const int next_tile = (int)misc[8];
+    __syncthreads();  // E: the reorder buffer and the tables are reused by the block's next tile
+    return next_tile;
 }
 
-// Persistent blocks: block b works on tiles b, b + gridDim.x, ...; the grid is sized so that all
-// blocks are resident at once, hence a tile only ever waits for tiles that already run.
+// Persistent blocks.  Tiles are handed out by an atomic ticket, in order, so a tile only ever
+// waits for tiles whose blocks already run: forward progress does not depend on how many
+// blocks of the grid are resident.
 template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, int pass, Digit dg,
-                TempHeader *hdr, const unsigned int *gbase_all, SW *status_all, int num_tiles) {
+                TempHeader *hdr, const unsigned long long *gbase_all, SW *status_all, int num_tiles, int value_seq) {
     constexpr int TILE = THREADS * ITEMS;
-    static_assert(THREADS >= kRadix, "one thread per digit");
+    static_assert(THREADS >= 2 * kRadix, "one thread per digit for the offsets and one for the look-back");
     using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
 
     if (hdr->reserved[kCtlSkip + pass]) return;
-    const bool src_is_alt = hdr->reserved[kCtlSrcIsAlt + pass] != 0;
-    PassContext<K, V, SW> c;
-    // Buffer 0 is the caller's (possibly strided) view, buffer 1 the dense alternate.
-    c.src = src_is_alt ? buf1 : buf0;
-    c.dst = src_is_alt ? buf0 : buf1;
-    c.src_stride = src_is_alt ? 1 : stride0;
-    c.dst_stride = src_is_alt ? stride0 : 1;
-    c.vsrc = src_is_alt ? val1 : val0;
-    c.vdst = src_is_alt ? val0 : val1;
-    c.n = n;
-    c.num_tiles = num_tiles;
-    c.dense = stride0 == 1;
-    c.hdr = hdr;
-    c.gbase = gbase_all + pass * kRadix;
-    // Two look-back arrays alternate between the passes that run; this pass clears the
-    // slots the next one will use (the previous pass, their last user, has completed).
-    c.status = status_all + (src_is_alt ? (size_t)num_tiles * kRadix : 0);
-    c.status_next = status_all + (src_is_alt ? 0 : (size_t)num_tiles * kRadix);
-
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    if constexpr (Digit::kUsesIndex) {
-        unsigned char *after_digits =
-            smem_raw + (size_t)TILE * L::STAGE + (size_t)(THREADS / 32) * kRadix * 8 + kRadix * 8 + 64 + TILE;
-        dg.stage(reinterpret_cast<K *>(after_digits + kRadix * 8), reinterpret_cast<int64_t *>(after_digits));
-    }
-
-    int tile = (int)blockIdx.x;
-    if (tile >= num_tiles) return;
-    {   // the lane masks of the ranking tables start at zero and are left at zero by every item
-        unsigned int *mask0 = reinterpret_cast<unsigned int *>(smem_raw + (size_t)TILE * L::STAGE) + (THREADS / 32) * kRadix;
-        unsigned int *mask1 = reinterpret_cast<unsigned int *>(smem_raw + L::base_bytes);
-        for (int i = threadIdx.x; i < (THREADS / 32) * kRadix; i += THREADS) {
-            mask0[i] = 0u;
-            if (kRankGroup >= 2) mask1[i] = 0u;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    // The pass description lives in shared memory: a dozen pointers that would otherwise sit
+    // in registers for the whole kernel.
+    static_assert(sizeof(PassContext<K, V, SW>) <= 128, "context slot");
+    PassContext<K, V, SW> &c = *reinterpret_cast<PassContext<K, V, SW> *>(smem_raw + L::off_context);
+    unsigned int *misc = reinterpret_cast<unsigned int *>(smem_raw + L::off_misc);
+    if (threadIdx.x == THREADS - 1) {
+        const bool src_is_alt = hdr->reserved[kCtlSrcIsAlt + pass] != 0;
+        // Buffer 0 is the caller's (possibly strided) view, buffer 1 the dense alternate.
+        c.src = src_is_alt ? buf1 : buf0;
+        c.dst = src_is_alt ? buf0 : buf1;
+        c.src_stride = src_is_alt ? 1 : stride0;
+        c.dst_stride = src_is_alt ? stride0 : 1;
+        c.vsrc = src_is_alt ? val1 : val0;
+        c.vdst = src_is_alt ? val0 : val1;
+        c.n = n;
+        c.num_tiles = num_tiles;
+        c.dense = stride0 == 1;
+        c.bulk = c.dense && ((uintptr_t)c.src % 16 == 0);
+        c.value_seq = hdr->reserved[kCtlFirstPass] == (unsigned int)pass ? value_seq : kSeqNone;
+        c.hdr = hdr;
+        c.ticket = &hdr->reserved[kCtlTicket + pass];
+        c.gbase = gbase_all + pass * kRadix;
+        // Two look-back arrays alternate between the passes that run; this pass clears the
+        // slots the next one will use (the previous pass, their last user, has completed).
+        c.status = status_all + (src_is_alt ? (size_t)num_tiles * kRadix : 0);
+        c.status_next = status_all + (src_is_alt ? 0 : (size_t)num_tiles * kRadix);
+        unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + L::off_misc + 64);
+        if (kSortTma) {
+            mbar_init(bar, 1u);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
+        misc[8] = (unsigned int)take_ticket<K, V, SW, TILE>(c, reinterpret_cast<K *>(smem_raw + L::off_stage), bar);
     }
-    K key[ITEMS];
-    load_tile_keys<K, V, SW, THREADS, ITEMS>(key, c, tile);
-    while (true) {
-        const int next_tile = tile + (int)gridDim.x;
-        if (c.dense && (int64_t)(tile + 1) * TILE <= n)
-            onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, true>(key, c, tile, next_tile, dg, smem_raw);
+    if constexpr (Digit::kUsesIndex)
+        dg.stage(reinterpret_cast<K *>(smem_raw + L::off_splitters + kRadix * 8),
+                 reinterpret_cast<int64_t *>(smem_raw + L::off_splitters));
+    __syncthreads();
+    int tile = (int)misc[8];
+    __syncthreads();  // misc[8] is written again during the first tile
+    const bool dense = stride0 == 1;
+    unsigned int bulk_phase = 0u;
+    while (tile < num_tiles) {
+        if (dense && (int64_t)(tile + 1) * TILE <= n)
+            tile = onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, true>(c, tile, bulk_phase, dg, smem_raw);
         else
-            onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, false>(key, c, tile, next_tile, dg, smem_raw);
-        if (next_tile >= num_tiles) break;
-        tile = next_tile;
+            tile = onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, false>(c, tile, bulk_phase, dg, smem_raw);
     }
 }
 
 // ---- 4. bring the result home when it ended in the alternate buffer ---------------------
 template <typename K, typename V>
 __global__ void __launch_bounds__(256)
-sort_copy_back_kernel(K *buf0, int64_t stride0, const K *buf1, V *val0, const V *val1, int64_t n, const TempHeader *hdr) {
-    if (!hdr->reserved[kCtlFinalInAlt]) return;
+sort_copy_back_kernel(K *buf0, int64_t stride0, const K *buf1, V *val0, const V *val1, int64_t n, const TempHeader *hdr,
+                      int value_seq) {
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    if constexpr (ValueBytes<V>::value != 0 && sizeof(V) <= 8) {
+        // no pass ran (every key equal): the keys stay where they are, the values still have to be made
+        if (value_seq != kSeqNone && hdr->reserved[kCtlFirstPass] == kNoPass)
+            for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) val0[i] = sequence_value<V>(value_seq, i);
+    }
+    if (!hdr->reserved[kCtlFinalInAlt]) return;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
         buf0[i * stride0] = buf1[i];
         if constexpr (ValueBytes<V>::value != 0) val0[i] = val1[i];
@@ -693,8 +708,8 @@ static SortLayout sort_layout(int key_bytes, int value_bytes, int64_t n) {
     L.tiles = ceil_div(n < 1 ? 1 : n, L.tile);
     L.wide_status = n >= (1ll << 30);
     L.off_ghist = sizeof(TempHeader);
-    L.off_gbase = L.off_ghist + (int64_t)kMaxPasses * kRadix * 4;
-    L.off_status = L.off_gbase + (int64_t)kMaxPasses * kRadix * 4;
+    L.off_gbase = L.off_ghist + (int64_t)kMaxPasses * kRadix * 8;
+    L.off_status = L.off_gbase + (int64_t)kMaxPasses * kRadix * 8;
     L.control_bytes = L.off_status + round_up(2 * L.tiles * kRadix * (L.wide_status ? 8 : 4), 256);
     L.off_keys = L.control_bytes;
     L.off_values = L.off_keys + round_up(n * key_bytes, 256);
@@ -703,26 +718,27 @@ static SortLayout sort_layout(int key_bytes, int value_bytes, int64_t n) {
 }
 
 // Opts the kernel in to its dynamic shared memory and asks how many of its blocks fit on one
-// SM; once per kernel instantiation, device and host thread.
+// SM; once per kernel instantiation and CUDA context (function attributes belong to a context).
 template <typename KernelT>
 static int configure_persistent(KernelT kernel, int threads, size_t bytes, int *blocks_per_sm) {
-    static thread_local int configured_device = -1;
-    static thread_local int cached_blocks = 0;
-    int dev = 0;
-    B200ALG_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_device != dev) {
+    static ContextCache<int> cache;
+    int blocks = 0;
+    if (!cache.find(&blocks)) {
         B200ALG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-        B200ALG_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&cached_blocks, kernel, threads, bytes));
-        if (cached_blocks < 1) return B200ALG_UNSUPPORTED;
-        configured_device = dev;
+        // all of the SM's L1 / shared-memory array as shared memory: two blocks need more than
+        // the split the driver would pick by itself
+        B200ALG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        B200ALG_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, threads, bytes));
+        if (blocks < 1) return B200ALG_UNSUPPORTED;
+        cache.store(blocks);
     }
-    *blocks_per_sm = cached_blocks;
+    *blocks_per_sm = blocks;
     return B200ALG_OK;
 }
 
 template <typename K, typename V, typename SW, typename XF>
 static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_t n, const KeyXform<K> &xf, void *temp,
-                      const SortLayout &L) {
+                      const SortLayout &L, int value_seq) {
     constexpr int THREADS = SortTuning<K>::THREADS, ITEMS = SortTuning<K>::ITEMS;
     using Smem = OnesweepSmem<K, V, false, THREADS, ITEMS>;
     auto kernel = onesweep_kernel<K, V, SW, RadixDigit<K, XF>, THREADS, ITEMS>;
@@ -735,8 +751,8 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
     const int grid = (int)(L.tiles < resident ? L.tiles : resident);
     char *t = (char *)temp;
     TempHeader *hdr = (TempHeader *)temp;
-    unsigned int *ghist = (unsigned int *)(t + L.off_ghist);
-    unsigned int *gbase = (unsigned int *)(t + L.off_gbase);
+    unsigned long long *ghist = (unsigned long long *)(t + L.off_ghist);
+    unsigned long long *gbase = (unsigned long long *)(t + L.off_gbase);
     SW *status = (SW *)(t + L.off_status);
     K *alt_keys = (K *)(t + L.off_keys);
     V *alt_vals = (V *)(t + L.off_values);
@@ -752,13 +768,12 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
         const int64_t cap = (int64_t)sm_count() * (histo_smem > 100 * 1024 ? 1 : 2);
         const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
         {
-            static thread_local int histo_device = -1;
-            int dev = 0;
-            B200ALG_CUDA_TRY(cudaGetDevice(&dev));
-            if (histo_device != dev) {
+            static ContextCache<int> opted_in;
+            int done = 0;
+            if (!opted_in.find(&done)) {
                 B200ALG_CUDA_TRY(cudaFuncSetAttribute(sort_histogram_kernel<K, kBigShift>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistoMaxSmem));
                 B200ALG_CUDA_TRY(cudaFuncSetAttribute(sort_histogram_kernel<K, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistoMaxSmem));
-                histo_device = dev;
+                opted_in.store(1);
             }
         }
         if (big)
@@ -767,21 +782,21 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
             sort_histogram_kernel<K, 3><<<blocks, kHistoThreads, histo_smem, s>>>(keys, stride, n, xf, ghist);
         B200ALG_LAUNCH_CHECK();
     }
-    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, L.passes, (unsigned int)n);
+    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, L.passes, (unsigned long long)n);
     B200ALG_LAUNCH_CHECK();
     for (int p = 0; p < L.passes; ++p) {
         RadixDigit<K, XF> dg;
         if constexpr (std::is_same<XF, KeyXform<K>>::value) dg.xf = xf;
         dg.shift = p * 8;
         kernel<<<grid, THREADS, Smem::bytes, s>>>(keys, stride, alt_keys, values, alt_vals, n, p, dg, hdr, gbase, status,
-                                                  (int)L.tiles);
+                                                  (int)L.tiles, value_seq);
         B200ALG_LAUNCH_CHECK();
     }
     {
         int64_t want = ceil_div(n, 256 * 8);
         const int64_t cap = (int64_t)sm_count() * 8;
         const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-        sort_copy_back_kernel<K, V><<<blocks, 256, 0, s>>>(keys, stride, alt_keys, values, alt_vals, n, hdr);
+        sort_copy_back_kernel<K, V><<<blocks, 256, 0, s>>>(keys, stride, alt_keys, values, alt_vals, n, hdr, value_seq);
         B200ALG_LAUNCH_CHECK();
     }
     return B200ALG_OK;
@@ -789,25 +804,25 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
 
 template <typename K, typename V>
 static int run_sort(cudaStream_t s, void *keys, int64_t stride, void *values, int64_t n, uint64_t xn, uint64_t xp,
-                    void *temp, const SortLayout &L) {
+                    void *temp, const SortLayout &L, int value_seq) {
     KeyXform<K> xf{(K)xn, (K)xp};
     const bool identity = xn == 0 && xp == 0;
     if (L.wide_status) {
-        if (identity) return run_passes<K, V, unsigned long long, KeyIdentity<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
-        return run_passes<K, V, unsigned long long, KeyXform<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
+        if (identity) return run_passes<K, V, unsigned long long, KeyIdentity<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L, value_seq);
+        return run_passes<K, V, unsigned long long, KeyXform<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L, value_seq);
     }
-    if (identity) return run_passes<K, V, unsigned int, KeyIdentity<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
-    return run_passes<K, V, unsigned int, KeyXform<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L);
+    if (identity) return run_passes<K, V, unsigned int, KeyIdentity<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L, value_seq);
+    return run_passes<K, V, unsigned int, KeyXform<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L, value_seq);
 }
 
 template <typename V>
 static int dispatch_key(cudaStream_t s, int key_bytes, void *keys, int64_t stride, void *values, int64_t n, uint64_t xn,
-                        uint64_t xp, void *temp, const SortLayout &L) {
+                        uint64_t xp, void *temp, const SortLayout &L, int value_seq) {
     switch (key_bytes) {
-    case 1: return run_sort<uint8_t, V>(s, keys, stride, values, n, xn, xp, temp, L);
-    case 2: return run_sort<uint16_t, V>(s, keys, stride, values, n, xn, xp, temp, L);
-    case 4: return run_sort<uint32_t, V>(s, keys, stride, values, n, xn, xp, temp, L);
-    case 8: return run_sort<uint64_t, V>(s, keys, stride, values, n, xn, xp, temp, L);
+    case 1: return run_sort<uint8_t, V>(s, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 2: return run_sort<uint16_t, V>(s, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 4: return run_sort<uint32_t, V>(s, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 8: return run_sort<uint64_t, V>(s, keys, stride, values, n, xn, xp, temp, L, value_seq);
     }
     return B200ALG_UNSUPPORTED;
 }
@@ -819,7 +834,7 @@ static int dispatch_key(cudaStream_t s, int key_bytes, void *keys, int64_t strid
 // than that are counted with shared-memory atomics on tables private to each warp.
 template <typename K>
 __global__ void __launch_bounds__(256)
-bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K> dg, unsigned int *ghist) {
+bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K> dg, unsigned long long *ghist) {
     __shared__ unsigned int sh[8][kRadix];
     __shared__ K staged_keys[kRadix];
     __shared__ int64_t staged_index[kRadix];
@@ -887,10 +902,10 @@ bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K>
     unsigned int c = 0;
 #pragma unroll
     for (int r = 0; r < 8; ++r) c += sh[r][threadIdx.x];
-    if (c) atomicAdd(ghist + threadIdx.x, c);
+    if (c) atomicAdd(ghist + threadIdx.x, (unsigned long long)c);
 }
 
-__global__ void export_bucket_counts_kernel(const unsigned int *ghist, int64_t *counts, int num_buckets) {
+__global__ void export_bucket_counts_kernel(const unsigned long long *ghist, int64_t *counts, int num_buckets) {
     if ((int)threadIdx.x < num_buckets) counts[threadIdx.x] = (int64_t)ghist[threadIdx.x];
 }
 
@@ -909,8 +924,8 @@ static int run_partition(cudaStream_t s, const K *keys, const V *values, int64_t
     const int grid = (int)(L.tiles < resident ? L.tiles : resident);
     char *t = (char *)temp;
     TempHeader *hdr = (TempHeader *)temp;
-    unsigned int *ghist = (unsigned int *)(t + L.off_ghist);
-    unsigned int *gbase = (unsigned int *)(t + L.off_gbase);
+    unsigned long long *ghist = (unsigned long long *)(t + L.off_ghist);
+    unsigned long long *gbase = (unsigned long long *)(t + L.off_gbase);
     SW *status = (SW *)(t + L.off_status);
     B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)L.control_bytes, s));
     {
@@ -922,12 +937,12 @@ static int run_partition(cudaStream_t s, const K *keys, const V *values, int64_t
     }
     // One "pass": offsets of the buckets; the skip rule is off (n + 1 never matches a count),
     // so the pass always moves the keys from buffer 0 (input) to buffer 1 (output).
-    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (unsigned int)n + 1u);
+    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (unsigned long long)n + 1ull);
     B200ALG_LAUNCH_CHECK();
     export_bucket_counts_kernel<<<1, kRadix, 0, s>>>(ghist, counts, num_buckets);
     B200ALG_LAUNCH_CHECK();
     kernel<<<grid, THREADS, Smem::bytes, s>>>(const_cast<K *>(keys), 1, out_keys, const_cast<V *>(values), out_values, n, 0,
-                                              dg, hdr, gbase, status, (int)L.tiles);
+                                              dg, hdr, gbase, status, (int)L.tiles, (int)kSeqNone);
     B200ALG_LAUNCH_CHECK();
     return B200ALG_OK;
 }
@@ -936,8 +951,8 @@ static int run_partition(cudaStream_t s, const K *keys, const V *values, int64_t
 template <typename K>
 static int run_bucket_count(cudaStream_t s, const K *keys, int64_t n, const SplitterBucket<K> &dg, int64_t *counts,
                             int num_buckets, void *temp, const SortLayout &L) {
-    unsigned int *ghist = (unsigned int *)((char *)temp + L.off_ghist);
-    B200ALG_CUDA_TRY(cudaMemsetAsync(ghist, 0, kRadix * sizeof(unsigned int), s));
+    unsigned long long *ghist = (unsigned long long *)((char *)temp + L.off_ghist);
+    B200ALG_CUDA_TRY(cudaMemsetAsync(ghist, 0, kRadix * sizeof(unsigned long long), s));
     int64_t want = ceil_div(n, 256 * 8);
     const int64_t cap = (int64_t)sm_count() * 8;
     const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
@@ -964,16 +979,16 @@ static int run_bucket_scatter(cudaStream_t s, const K *keys, const V *values, in
     const int grid = (int)(L.tiles < resident ? L.tiles : resident);
     char *t = (char *)temp;
     TempHeader *hdr = (TempHeader *)temp;
-    unsigned int *ghist = (unsigned int *)(t + L.off_ghist);
-    unsigned int *gbase = (unsigned int *)(t + L.off_gbase);
+    unsigned long long *ghist = (unsigned long long *)(t + L.off_ghist);
+    unsigned long long *gbase = (unsigned long long *)(t + L.off_gbase);
     SW *status = (SW *)(t + L.off_status);
     B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)L.control_bytes, s));
     // all-zero histogram: the bucket offsets come out zero (every bucket has its own base
     // pointer) and the pass is scheduled from buffer 0
-    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (unsigned int)n + 1u);
+    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (unsigned long long)n + 1ull);
     B200ALG_LAUNCH_CHECK();
     kernel<<<grid, THREADS, Smem::bytes, s>>>(const_cast<K *>(keys), 1, nullptr, const_cast<V *>(values), nullptr, n, 0, dg, hdr,
-                                              gbase, status, (int)L.tiles);
+                                              gbase, status, (int)L.tiles, (int)kSeqNone);
     B200ALG_LAUNCH_CHECK();
     return B200ALG_OK;
 }
@@ -1009,7 +1024,7 @@ static int bucket_ops(void *stream, bool scatter, const void *keys, const void *
     if (num_splitters && (!splitter_keys || !splitter_index)) return B200ALG_INVALID_ARGUMENT;
     const int kb = dtype_bytes(key_dtype);
     if (kb == 0) return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
     if (((uintptr_t)keys % kb) || ((uintptr_t)temp % 256)) return B200ALG_MISALIGNED;
     uint64_t xn, xp;
     if (!key_xform_constants(key_dtype, order, xn, xp)) return B200ALG_UNSUPPORTED;
@@ -1057,7 +1072,7 @@ static int partition_key(cudaStream_t s, int kb, const void *keys, const void *v
 }
 
 static int sort_common(void *stream, void *keys, int64_t stride, void *values, int64_t n, int key_dtype, int value_bytes,
-                       int order, void *temp, int64_t temp_bytes) {
+                       int order, void *temp, int64_t temp_bytes, int value_seq = kSeqNone) {
     // Argument checks mirror VerifyArguments (RadixSortExtensions.cs:1340-1367).
     if (!keys || !temp || (value_bytes && !values)) return B200ALG_INVALID_ARGUMENT;
     if (n < 0 || stride < 1) return B200ALG_INVALID_ARGUMENT;
@@ -1065,7 +1080,7 @@ static int sort_common(void *stream, void *keys, int64_t stride, void *values, i
     if (kb == 0) return B200ALG_UNSUPPORTED;
     if (value_bytes != 0 && value_bytes != 1 && value_bytes != 2 && value_bytes != 4 && value_bytes != 8 && value_bytes != 16)
         return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
     if (((uintptr_t)keys % kb) || (value_bytes && ((uintptr_t)values % value_bytes)) || ((uintptr_t)temp % 256))
         return B200ALG_MISALIGNED;
     uint64_t xn, xp;
@@ -1075,12 +1090,12 @@ static int sort_common(void *stream, void *keys, int64_t stride, void *values, i
     if (n == 0) return B200ALG_OK;
     cudaStream_t s = (cudaStream_t)stream;
     switch (value_bytes) {
-    case 0: return dispatch_key<NoValue>(s, kb, keys, stride, values, n, xn, xp, temp, L);
-    case 1: return dispatch_key<uint8_t>(s, kb, keys, stride, values, n, xn, xp, temp, L);
-    case 2: return dispatch_key<uint16_t>(s, kb, keys, stride, values, n, xn, xp, temp, L);
-    case 4: return dispatch_key<uint32_t>(s, kb, keys, stride, values, n, xn, xp, temp, L);
-    case 8: return dispatch_key<uint64_t>(s, kb, keys, stride, values, n, xn, xp, temp, L);
-    case 16: return dispatch_key<uint4>(s, kb, keys, stride, values, n, xn, xp, temp, L);
+    case 0: return dispatch_key<NoValue>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 1: return dispatch_key<uint8_t>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 2: return dispatch_key<uint16_t>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 4: return dispatch_key<uint32_t>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 8: return dispatch_key<uint64_t>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 16: return dispatch_key<uint4>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
     }
     return B200ALG_UNSUPPORTED;
 }
@@ -1093,7 +1108,7 @@ extern "C" int b200alg_radix_sort_temp_bytes(int key_dtype, int64_t n, int value
     if (!out_bytes || n < 0 || value_bytes < 0) return B200ALG_INVALID_ARGUMENT;
     const int kb = dtype_bytes(key_dtype);
     if (kb == 0) return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
     *out_bytes = sort_layout(kb, value_bytes, n).total;
     return B200ALG_OK;
 }
@@ -1109,11 +1124,19 @@ extern "C" int b200alg_radix_sort_pairs(void *stream, void *keys, void *values, 
     return sort_common(stream, keys, 1, values, n, key_dtype, value_bytes, order, temp, temp_bytes);
 }
 
+extern "C" int b200alg_radix_sort_pairs_sequence(void *stream, void *keys, void *values, int64_t n, int key_dtype,
+                                                 int value_dtype, int order, void *temp, int64_t temp_bytes) {
+    const int vb = dtype_bytes(value_dtype);
+    if (vb == 0) return B200ALG_UNSUPPORTED;
+    const bool floating = value_dtype == B200ALG_F16 || value_dtype == B200ALG_F32 || value_dtype == B200ALG_F64;
+    return sort_common(stream, keys, 1, values, n, key_dtype, vb, order, temp, temp_bytes, floating ? kSeqFloating : kSeqInteger);
+}
+
 extern "C" int b200alg_bucket_partition_temp_bytes(int key_dtype, int64_t n, int64_t *out_bytes) {
     if (!out_bytes || n < 0) return B200ALG_INVALID_ARGUMENT;
     const int kb = dtype_bytes(key_dtype);
     if (kb == 0) return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
     *out_bytes = sort_layout(kb, 0, n).control_bytes;
     return B200ALG_OK;
 }
@@ -1130,7 +1153,7 @@ extern "C" int b200alg_bucket_partition(void *stream, const void *keys, const vo
     const int kb = dtype_bytes(key_dtype);
     if (kb == 0) return B200ALG_UNSUPPORTED;
     if (value_bytes != 0 && value_bytes != 4 && value_bytes != 8) return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
     if (((uintptr_t)keys % kb) || ((uintptr_t)out_keys % kb) || ((uintptr_t)temp % 256) || ((uintptr_t)bucket_counts % 8))
         return B200ALG_MISALIGNED;
     uint64_t xn, xp;
@@ -1152,13 +1175,6 @@ extern "C" int b200alg_bucket_partition(void *stream, const void *keys, const vo
     }
     return B200ALG_UNSUPPORTED;
 }
-
-#ifdef B200ALG_EXP_TIMING
-extern "C" int b200alg_exp_set_debug(void *ptr) {
-    B200ALG_CUDA_TRY(cudaMemcpyToSymbol(b200alg::g_exp_debug, &ptr, sizeof(ptr)));
-    return B200ALG_OK;
-}
-#endif
 
 extern "C" int b200alg_bucket_count(void *stream, const void *keys, int64_t n, int key_dtype, int order,
                                     const void *splitter_keys, const int64_t *splitter_index, int num_splitters,

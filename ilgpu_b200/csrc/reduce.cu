@@ -49,7 +49,13 @@ template <int OP> struct AtomicApply<double, OP> {
     }
 };
 
-template <typename T> __global__ void set_scalar_kernel(T *out, T v) { *out = v; }
+// out[0] = Identity.  The reduction kernel is launched as a programmatic dependent of this
+// one: its blocks fold their share of the input while this kernel runs and wait for it only
+// before they combine into out[0].
+template <typename T> __global__ void set_scalar_kernel(T *out, T v) {
+    grid_dependency_release();
+    *out = v;
+}
 
 template <typename T, int OP, int THREADS>
 __device__ __forceinline__ void block_fold_and_publish(T acc, T *out) {
@@ -63,7 +69,10 @@ __device__ __forceinline__ void block_fold_and_publish(T acc, T *out) {
         T v = threadIdx.x < THREADS / 32 ? warp_part[threadIdx.x] : O::identity();
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) v = O::apply(v, shfl_down(v, d));
-        if (threadIdx.x == 0) AtomicApply<T, OP>::run(out, v);
+        if (threadIdx.x == 0) {
+            grid_dependency_wait();  // out[0] holds Identity from here on
+            AtomicApply<T, OP>::run(out, v);
+        }
     }
 }
 
@@ -133,11 +142,11 @@ static int launch_reduce(cudaStream_t s, const void *in, int64_t stride, int64_t
     if (stride == 1) {
         int64_t want = ceil_div(n, (int64_t)THREADS * VEC * 4);
         int blocks = (int)(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
-        reduce_dense_kernel<T, OP, THREADS><<<blocks, THREADS, 0, s>>>((const T *)in, n, (T *)out);
+        B200ALG_CUDA_TRY(launch_dependent(reduce_dense_kernel<T, OP, THREADS>, dim3(blocks), dim3(THREADS), 0, s, (const T *)in, n, (T *)out));
     } else {
         int64_t want = ceil_div(n, (int64_t)THREADS * 4);
         int blocks = (int)(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
-        reduce_strided_kernel<T, OP, THREADS><<<blocks, THREADS, 0, s>>>((const T *)in, stride, n, (T *)out);
+        B200ALG_CUDA_TRY(launch_dependent(reduce_strided_kernel<T, OP, THREADS>, dim3(blocks), dim3(THREADS), 0, s, (const T *)in, stride, n, (T *)out));
     }
     B200ALG_LAUNCH_CHECK();
     return B200ALG_OK;

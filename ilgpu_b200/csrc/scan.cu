@@ -8,65 +8,42 @@
 
 namespace b200alg {
 
-#ifndef B200ALG_SCAN_THREADS
-#define B200ALG_SCAN_THREADS 256
-#endif
-#ifndef B200ALG_SCAN_VEC
-#define B200ALG_SCAN_VEC 8
-#endif
-#ifndef B200ALG_SCAN_MIN_BLOCKS
-#define B200ALG_SCAN_MIN_BLOCKS 1
-#endif
-constexpr int kScanThreads = B200ALG_SCAN_THREADS;
+constexpr int kScanThreads = 256;
 constexpr int kScanWarps = kScanThreads / 32;
-constexpr int kScanVecPerThread = B200ALG_SCAN_VEC;  // 8 x 16 bytes per thread -> 32 KB per tile
+constexpr int kScanVecPerThread = 8;  // 8 x 16 bytes per thread -> 32 KB per tile
 
 constexpr int kScanMinTileElems = 2 * kScanVecPerThread * kScanThreads;  // tile of an 8-byte type
 
-__device__ __forceinline__ int swz(int slot) { return slot ^ ((slot >> 3) & 7); }
-
-template <typename T, int OP, bool INCLUSIVE, bool VECTOR>
-__global__ void __launch_bounds__(kScanThreads, B200ALG_SCAN_MIN_BLOCKS)
+// General variant (strided or unaligned views): one tile per block, handed out by an atomic
+// ticket, guarded element loads; thread t holds ITEMS consecutive elements of the tile.
+template <typename T, int OP, bool INCLUSIVE>
+__global__ void __launch_bounds__(kScanThreads)
 scan_kernel(const T *in, int64_t in_stride, T *out, int64_t out_stride, int64_t n, const T *carry_in,
             TempHeader *hdr, void *state_base, int num_tiles) {
     using O = Op<T, OP>;
     constexpr int VEC = 16 / sizeof(T);
     constexpr int ITEMS = VEC * kScanVecPerThread;
     constexpr int TILE = ITEMS * kScanThreads;
-    union Items { uint4 v[kScanVecPerThread]; T t[ITEMS]; };
+    struct Items { T t[ITEMS]; };
 
-    __shared__ uint4 xchg[kScanWarps][32 * kScanVecPerThread];
     __shared__ T warp_total[kScanWarps];
     __shared__ T warp_excl[kScanWarps];
     __shared__ T s_prefix;
     __shared__ int s_tile;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    grid_dependency_wait();  // the descriptors and the ticket counter have been cleared
     if (tid == 0) s_tile = (int)atomicAdd(&hdr->reserved[0], 1u);
     __syncthreads();
     const int tile = s_tile;
     const int64_t base = (int64_t)tile * TILE;
     const int64_t remaining = n - base;
-    const bool full = remaining >= TILE;
 
     Items it;
-    if (VECTOR && full) {
-        // Warp-striped 128-bit loads, then a warp-local transposition through swizzled
-        // shared memory so that each thread holds ITEMS consecutive elements.
-        const uint4 *src = reinterpret_cast<const uint4 *>(in + base) + warp * (32 * kScanVecPerThread);
 #pragma unroll
-        for (int j = 0; j < kScanVecPerThread; ++j) it.v[j] = __ldcs(src + j * 32 + lane);
-#pragma unroll
-        for (int j = 0; j < kScanVecPerThread; ++j) xchg[warp][swz(j * 32 + lane)] = it.v[j];
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < kScanVecPerThread; ++j) it.v[j] = xchg[warp][swz(lane * kScanVecPerThread + j)];
-    } else {
-#pragma unroll
-        for (int k = 0; k < ITEMS; ++k) {
-            const int64_t idx = (int64_t)tid * ITEMS + k;
-            it.t[k] = idx < remaining ? in[(base + idx) * in_stride] : O::identity();
-        }
+    for (int k = 0; k < ITEMS; ++k) {
+        const int64_t idx = (int64_t)tid * ITEMS + k;
+        it.t[k] = idx < remaining ? in[(base + idx) * in_stride] : O::identity();
     }
 
     // Thread total -> warp scan -> block scan.
@@ -155,67 +132,31 @@ scan_kernel(const T *in, int64_t in_stride, T *out, int64_t out_stride, int64_t 
         }
     }
 
-    if (VECTOR && full) {
-        __syncwarp();
 #pragma unroll
-        for (int j = 0; j < kScanVecPerThread; ++j) xchg[warp][swz(lane * kScanVecPerThread + j)] = it.v[j];
-        __syncwarp();
-        uint4 *dst = reinterpret_cast<uint4 *>(out + base) + warp * (32 * kScanVecPerThread);
-#pragma unroll
-        for (int j = 0; j < kScanVecPerThread; ++j) __stcs(dst + j * 32 + lane, xchg[warp][swz(j * 32 + lane)]);
-    } else {
-#pragma unroll
-        for (int k = 0; k < ITEMS; ++k) {
-            const int64_t idx = (int64_t)tid * ITEMS + k;
-            if (idx < remaining) out[(base + idx) * out_stride] = it.t[k];
-        }
+    for (int k = 0; k < ITEMS; ++k) {
+        const int64_t idx = (int64_t)tid * ITEMS + k;
+        if (idx < remaining) out[(base + idx) * out_stride] = it.t[k];
     }
 }
 
+// Clears the control block and the tile descriptors a scan is about to use.  The scan kernel
+// is launched as a programmatic dependent of this one, so its blocks are already resident
+// (barriers initialised) when the last descriptor has been cleared.
+__global__ void __launch_bounds__(256) scan_clear_kernel(uint4 *words, int64_t count) {
+    grid_dependency_release();
+    const int64_t step = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < count; i += step) words[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 // ---- pipelined variant for dense, 16-byte aligned views ---------------------------------
-// Persistent blocks take tiles round-robin (tile = blockIdx.x + k * gridDim.x); all blocks
-// of the grid are resident at once, so a tile only ever waits for tiles that already run.
+// Persistent blocks take tiles from an atomic ticket counter, in order and one per ring stage
+// ahead, so a tile only ever waits for tiles whose blocks already run: forward progress does
+// not depend on how many blocks of the grid are resident.
 // The input of the next tiles is staged into a shared-memory ring by bulk asynchronous
 // copies (TMA, one elected thread, completion on an mbarrier), which keeps loads in flight
 // while a block is busy with the scan and the look-back of its current tile.
-#ifndef B200ALG_SCAN_STAGES
-#define B200ALG_SCAN_STAGES 2
-#endif
-constexpr int kScanStages = B200ALG_SCAN_STAGES;
+constexpr int kScanStages = 2;
 constexpr int kScanTileBytes = kScanThreads * kScanVecPerThread * 16;
-constexpr unsigned int kMaxBarrierPolls = 1u << 22;
-
-__device__ __forceinline__ unsigned int smem_addr(const void *p) { return (unsigned int)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned int bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned int parity) {
-    unsigned int ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_addr(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bulk copy global -> this block's shared memory (no multicast); both addresses and the size
-// are multiples of 16 bytes.
-__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, unsigned int bytes, unsigned long long *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(smem_dst)),
-                 "l"(gsrc), "r"(bytes), "r"(smem_addr(bar))
-                 : "memory");
-}
-// Bounded wait; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned int parity) {
-    for (unsigned int polls = 0; polls < kMaxBarrierPolls; ++polls)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
 
 template <typename T, int OP, bool INCLUSIVE>
 __global__ void __launch_bounds__(kScanThreads)
@@ -231,20 +172,25 @@ scan_pipeline_kernel(const T *in, T *out, int64_t n, const T *carry_in, TempHead
     __shared__ T warp_total[kScanWarps];
     __shared__ T warp_excl[kScanWarps];
     __shared__ T s_prefix;
+    __shared__ int s_ticket[kScanStages];  // tile that each ring stage is for
+    __shared__ int s_staged[kScanStages];  // 1 = a bulk copy of that tile's input into the stage was issued
+    __shared__ int s_failed;               // a wait for a bulk copy ran out: later tiles are loaded directly
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int G = (int)gridDim.x;
     const int full_tiles = (int)(n / TILE);  // tiles below this index are complete
 
+    unsigned int in_flight = 0;  // thread 0: bit st set = a copy into stage st has not been waited for
     if (tid == 0) {
+        s_failed = 0;
         for (int st = 0; st < kScanStages; ++st) mbar_init(&full_bar[st], 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();
-    unsigned int in_flight = 0;  // thread 0: bit st set = a copy into stage st has not been waited for
+    grid_dependency_wait();  // the descriptors and the ticket counter have been cleared
     if (tid == 0) {
         for (int st = 0; st < kScanStages; ++st) {
-            const int t = (int)blockIdx.x + st * G;
+            const int t = (int)atomicAdd(&hdr->reserved[0], 1u);
+            s_ticket[st] = t;
+            s_staged[st] = t < full_tiles;
             if (t < full_tiles) {
                 mbar_expect_tx(&full_bar[st], kScanTileBytes);
                 bulk_load(ring + st * kScanTileBytes, in + (int64_t)t * TILE, kScanTileBytes, &full_bar[st]);
@@ -252,20 +198,23 @@ scan_pipeline_kernel(const T *in, T *out, int64_t n, const T *carry_in, TempHead
             }
         }
     }
-    bool failed = false;
+    __syncthreads();
+    unsigned int bar_phase = 0;  // bit st = parity of the next completion of stage st's barrier
     TileState<T> state(state_base, num_tiles);
 
-    int k = 0;
-    for (int tile = (int)blockIdx.x; tile < num_tiles; tile += G, ++k) {
+    for (int k = 0;; ++k) {
         const int st = k % kScanStages;
-        const unsigned int parity = (unsigned int)(k / kScanStages) & 1u;
+        const int tile = s_ticket[st];
+        if (tile >= num_tiles) break;  // tickets ascend: every later one is beyond the end too
         const int64_t base = (int64_t)tile * TILE;
         const bool full = tile < full_tiles;
+        const bool staged = s_staged[st] != 0;
 
         // Vector j of lane l covers elements (warp*32*NV + j*32 + l) * VEC ... + VEC of the tile.
         Vec v[NV];
-        if (full) {
-            if (!mbar_wait(&full_bar[st], parity)) failed = true;
+        if (staged) {
+            if (!mbar_wait(&full_bar[st], (bar_phase >> st) & 1u)) s_failed = 1;
+            bar_phase ^= 1u << st;
             const uint4 *src = reinterpret_cast<const uint4 *>(ring + st * kScanTileBytes) + warp * (32 * NV);
 #pragma unroll
             for (int j = 0; j < NV; ++j) v[j].u = src[j * 32 + lane];
@@ -308,9 +257,12 @@ scan_pipeline_kernel(const T *in, T *out, int64_t n, const T *carry_in, TempHead
         if (lane == 31) warp_total[warp] = chunk;
         __syncthreads();  // warp totals are visible; every thread has taken its data out of the ring
 
-        if (tid == 0 && !failed) {
-            const int t2 = tile + kScanStages * G;
-            if (t2 < full_tiles) {
+        if (tid == 0) {
+            const int t2 = (int)atomicAdd(&hdr->reserved[0], 1u);
+            const bool stage_it = t2 < full_tiles && !s_failed;
+            s_ticket[st] = t2;
+            s_staged[st] = stage_it;
+            if (stage_it) {
                 mbar_expect_tx(&full_bar[st], kScanTileBytes);
                 bulk_load(ring + st * kScanTileBytes, in + (int64_t)t2 * TILE, kScanTileBytes, &full_bar[st]);
                 in_flight |= 1u << st;
@@ -339,14 +291,8 @@ scan_pipeline_kernel(const T *in, T *out, int64_t n, const T *carry_in, TempHead
                 // Decoupled look-back over kLookWays * 32 predecessors per round: lane l polls
                 // the tiles at distances l+1, l+33, ... so that several loads are in flight per
                 // lane; the operations are commutative, so the round's values are simply folded.
-#ifndef B200ALG_SCAN_LOOK_WAYS
-#define B200ALG_SCAN_LOOK_WAYS 1
-#endif
-                constexpr int kLookWays = B200ALG_SCAN_LOOK_WAYS;
-#ifndef B200ALG_SCAN_LOOK_LANES
-#define B200ALG_SCAN_LOOK_LANES 32
-#endif
-                constexpr int kLookLanes = kLookWays > 1 ? 32 : B200ALG_SCAN_LOOK_LANES;
+                constexpr int kLookWays = 1;
+                constexpr int kLookLanes = 32;
                 prefix = O::identity();
                 int look = tile - 1 - lane;
                 bool gave_up = false;
@@ -423,7 +369,8 @@ scan_pipeline_kernel(const T *in, T *out, int64_t n, const T *carry_in, TempHead
 
     // A barrier wait that ran out is reported; copies that may still be in flight are given
     // one more bounded wait so that the block does not retire underneath them.
-    if (__syncthreads_or(failed)) {
+    __syncthreads();
+    if (s_failed) {
         if (tid == 0) {
             atomicExch(&hdr->wait_limit_hit, 1u);
             for (int st = 0; st < kScanStages; ++st)
@@ -453,28 +400,34 @@ static int launch_scan(cudaStream_t s, const void *in, int64_t in_stride, void *
     TempHeader *hdr = (TempHeader *)temp;
     void *state = (char *)temp + sizeof(TempHeader);
     const size_t state_bytes = (size_t)tiles * kDescStride;
-    B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, sizeof(TempHeader) + state_bytes, s));
+    {
+        const int64_t words = (int64_t)((sizeof(TempHeader) + state_bytes) / 16);
+        const int64_t want = ceil_div(words, 256 * 4);
+        const int64_t cap = (int64_t)sm_count() * 4;
+        scan_clear_kernel<<<(int)(want < 1 ? 1 : (want > cap ? cap : want)), 256, 0, s>>>((uint4 *)temp, words);
+        B200ALG_LAUNCH_CHECK();
+    }
     const bool vec = in_stride == 1 && out_stride == 1 && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
     if (vec) {
         auto kernel = scan_pipeline_kernel<T, OP, INCLUSIVE>;
         constexpr size_t ring_bytes = (size_t)kScanStages * kScanTileBytes;
-        static thread_local int configured_device = -1;
-        static thread_local int blocks_per_sm = 0;
-        int dev = 0;
-        B200ALG_CUDA_TRY(cudaGetDevice(&dev));
-        if (configured_device != dev) {
+        static ContextCache<int> cache;  // per kernel instantiation and CUDA context
+        int blocks_per_sm = 0;
+        if (!cache.find(&blocks_per_sm)) {
             B200ALG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring_bytes));
             B200ALG_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, kernel, kScanThreads, ring_bytes));
             if (blocks_per_sm < 1) return B200ALG_UNSUPPORTED;
-            configured_device = dev;
+            cache.store(blocks_per_sm);
         }
-        // every block of the grid must be resident at the same time (tiles are taken round-robin)
+        // one wave of persistent blocks; tiles are handed out by ticket
         const int resident = sm_count() * blocks_per_sm;
         const int blocks = tiles < resident ? tiles : resident;
-        kernel<<<blocks, kScanThreads, ring_bytes, s>>>((const T *)in, (T *)out, n, (const T *)carry_in, hdr, state, tiles);
-    } else
-        scan_kernel<T, OP, INCLUSIVE, false><<<tiles, kScanThreads, 0, s>>>((const T *)in, in_stride, (T *)out, out_stride, n, (const T *)carry_in, hdr, state, tiles);
-    B200ALG_LAUNCH_CHECK();
+        B200ALG_CUDA_TRY(launch_dependent(kernel, dim3(blocks), dim3(kScanThreads), ring_bytes, s, (const T *)in, (T *)out, n,
+                                          (const T *)carry_in, hdr, state, tiles));
+    } else {
+        B200ALG_CUDA_TRY(launch_dependent(scan_kernel<T, OP, INCLUSIVE>, dim3(tiles), dim3(kScanThreads), 0, s, (const T *)in,
+                                          in_stride, (T *)out, out_stride, n, (const T *)carry_in, hdr, state, tiles));
+    }
     return B200ALG_OK;
 }
 
@@ -503,7 +456,7 @@ using namespace b200alg;
 extern "C" int b200alg_scan_temp_bytes(int dtype, int64_t n, int64_t *out_bytes) {
     if (!out_bytes || n < 0) return B200ALG_INVALID_ARGUMENT;
     if (!is_atomic_numeric(dtype)) return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
     *out_bytes = scan_temp_bytes_for(dtype, n);
     return B200ALG_OK;
 }
@@ -515,7 +468,7 @@ extern "C" int b200alg_scan_carry(void *stream, const void *in, int64_t in_strid
     if (!in || !out || !temp) return B200ALG_INVALID_ARGUMENT;
     if (n < 0 || in_stride < 1 || out_stride < 1) return B200ALG_INVALID_ARGUMENT;
     if (!is_atomic_numeric(dtype)) return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
     const int es = dtype_bytes(dtype);
     if (((uintptr_t)in % es) || ((uintptr_t)out % es) || (carry_in && ((uintptr_t)carry_in % es))) return B200ALG_MISALIGNED;
     if ((uintptr_t)temp % 256) return B200ALG_MISALIGNED;
@@ -548,21 +501,20 @@ constexpr int64_t kStaticScanMaxElements = 1ll << 26;
 constexpr size_t kStaticScanScratchBytes = sizeof(TempHeader) + (size_t)(kStaticScanMaxElements / kScanMinTileElems) * kDescStride;
 static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScanScratchBytes];
 
-// Device address of the array on the current device.  The array's name is only a handle on
-// the host side, so the address is asked for once per device, with that device current.
-static int static_scan_scratch(void **out) {
-    static void *address[64] = {nullptr};
-    int dev = 0;
-    B200ALG_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return B200ALG_UNSUPPORTED;
-    if (address[dev] == nullptr) {
-        void *p = nullptr;
+namespace b200alg {
+// Device address of the array in the current CUDA context.  The array's name is only a handle
+// on the host side, so the address is asked for once per context, with that context current.
+int static_scan_scratch(void **out) {
+    static ContextCache<void *> cache;
+    void *p = nullptr;
+    if (!cache.find(&p)) {
         B200ALG_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scan_scratch));
-        address[dev] = p;
+        cache.store(p);
     }
-    *out = address[dev];
+    *out = p;
     return B200ALG_OK;
 }
+}  // namespace b200alg
 
 extern "C" int b200alg_scan_static(void *stream, const void *in, int64_t in_stride, void *out, int64_t out_stride,
                                    int64_t n, int dtype, int op, int inclusive) {

@@ -173,7 +173,7 @@ extern "C" int b200alg_unique_temp_bytes(int dtype, int64_t n, int64_t *out_byte
     if (!out_bytes || n < 0) return B200ALG_INVALID_ARGUMENT;
     const int es = dtype_bytes(dtype);
     if (es == 0) return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
     *out_bytes = unique_layout(es, n).total;
     return B200ALG_OK;
 }
@@ -189,7 +189,7 @@ extern "C" int b200alg_unique(void *stream, void *data, int64_t n, int dtype, vo
     if (!data || !temp) return B200ALG_INVALID_ARGUMENT;
     const int es = dtype_bytes(dtype);
     if (es == 0) return B200ALG_UNSUPPORTED;
-    if (n > INT32_MAX) return B200ALG_TOO_LARGE;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
     if (((uintptr_t)data % es) || ((uintptr_t)out_count % 8) || ((uintptr_t)temp % 256)) return B200ALG_MISALIGNED;
     const UniqueLayout L = unique_layout(es, n);
     if (temp_bytes < L.total) return B200ALG_TEMP_TOO_SMALL;

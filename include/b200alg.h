@@ -63,7 +63,7 @@ typedef enum {
     B200ALG_CUDA_ERROR = 4,         /* see b200alg_last_cuda_error() */
     B200ALG_WAIT_LIMIT = 5,         /* a device-side wait ran out (reported by b200alg_device_status) */
     B200ALG_MISALIGNED = 6,         /* a pointer is not aligned to its element size / temp not to 256 */
-    B200ALG_TOO_LARGE = 7,          /* n beyond INT32_MAX (ErrorMessages.NotSupportedArrayView64) */
+    B200ALG_TOO_LARGE = 7,          /* n beyond 2^38; the int.MaxValue limit of the reference (ErrorMessages.NotSupportedArrayView64) is the host mirror's check */
     B200ALG_STATIC_LIMIT = 8        /* n beyond what an entry point with built-in scratch accepts */
 } b200alg_status;
 
@@ -89,6 +89,18 @@ int b200alg_radix_sort_keys(void *stream, void *keys, int64_t n, int64_t stride,
 /* values: n dense elements of value_bytes (1, 2, 4, 8 or 16) each, permuted like the keys. */
 int b200alg_radix_sort_pairs(void *stream, void *keys, void *values, int64_t n, int key_dtype,
                              int value_bytes, int order, void *temp, int64_t temp_bytes);
+
+/* The sequencer overload of CreateRadixSortPairs (RadixSortExtensions.cs:1017-1074, gather
+ * kernel :605-625): the values that enter the sort are not read from `values` but made
+ * from the element index by one of the reference's built-in sequencers - (T)i for the
+ * integer types (IndexSequencer, Sequencer.cs:37-42; {Int8..UInt64}Sequencer,
+ * Sequencers.tt:26-38), the converted index for F16 / F32 / F64 (Half-, Float-,
+ * DoubleSequencer, Sequencer.cs:47-72) - inside the first digit pass, so "payload =
+ * original index" costs neither a fill pass nor a read of the value view.  `values`
+ * (n dense elements of value_dtype) only receives the permuted result.  Temp size: that of
+ * b200alg_radix_sort_temp_bytes with value_bytes = the size of value_dtype. */
+int b200alg_radix_sort_pairs_sequence(void *stream, void *keys, void *values, int64_t n, int key_dtype,
+                                      int value_dtype, int order, void *temp, int64_t temp_bytes);
 
 /* Stable partition of a shard into num_splitters + 1 buckets: the first step of a sort
  * that spans several GPUs (new surface; the reference has no multi-device sort, its only

@@ -300,6 +300,44 @@ inline RadixSortPairs<TKey, TValue> CreateRadixSortPairs(const Accelerator &acce
     };
 }
 
+// Sequencers (Sequencer.cs:20-72, Sequencers.tt:26-38): element i is the index converted to T.
+// Only these built-in, stateless ones cross the native boundary.
+template <typename TValue> struct ISequencer { using T = TValue; };
+struct IndexSequencer : ISequencer<int32_t> {};
+struct Int8Sequencer : ISequencer<int8_t> {};
+struct UInt8Sequencer : ISequencer<uint8_t> {};
+struct Int16Sequencer : ISequencer<int16_t> {};
+struct UInt16Sequencer : ISequencer<uint16_t> {};
+struct Int32Sequencer : ISequencer<int32_t> {};
+struct UInt32Sequencer : ISequencer<uint32_t> {};
+struct Int64Sequencer : ISequencer<int64_t> {};
+struct UInt64Sequencer : ISequencer<uint64_t> {};
+struct FloatSequencer : ISequencer<float> {};
+struct DoubleSequencer : ISequencer<double> {};
+
+// The sequencer overload of CreateRadixSortPairs (RadixSortExtensions.cs:1017-1074): values
+// entering the sort are sequencer.ComputeSequenceElement(i); `values` receives the result.
+template <typename TKey, typename TValue, typename TSequencer>
+using RadixSortPairsSequenced =
+    std::function<void(const AcceleratorStream &, ArrayView1D<TKey>, ArrayView1D<TValue>, TSequencer, ArrayView<int>)>;
+template <typename TKey, typename TValue, typename TSequencer, typename TRadixSortOperation>
+inline RadixSortPairsSequenced<TKey, TValue, TSequencer> CreateRadixSortPairs(const Accelerator &accelerator) {
+    static_assert(std::is_same<TKey, typename TRadixSortOperation::T>::value, "operation and key type differ");
+    static_assert(std::is_same<TValue, typename TSequencer::T>::value, "sequencer and value type differ");
+    return [accelerator](const AcceleratorStream &stream, ArrayView1D<TKey> keys, ArrayView1D<TValue> values, TSequencer,
+                         ArrayView<int> temp) {
+        if (!keys.IsValid()) throw ArgumentNullException("keys");
+        if (!values.IsValid()) throw ArgumentNullException("values");
+        if (keys.Length != values.Length) throw ArgumentOutOfRangeException("values");
+        if (keys.Length > std::numeric_limits<int32_t>::max()) throw NotSupportedException("NotSupportedArrayView64");
+        detail::CheckTemp(temp, ComputeRadixSortPairsTempStorageSize<TKey, TValue, TRadixSortOperation>(accelerator, keys.Length));
+        accelerator.Bind();
+        B200AlgException::ThrowIfFailed(b200alg_radix_sort_pairs_sequence(
+            stream.StreamPtr(), keys.BaseView.Pointer, values.BaseView.Pointer, keys.Length, DTypeOf<TKey>::value,
+            DTypeOf<TValue>::value, TRadixSortOperation::Order, temp.Pointer, temp.LengthInBytes()));
+    };
+}
+
 // RadixSortProvider (RadixSortExtensions.cs:168-300): owns the temp buffer.
 class RadixSortProvider {
 public:

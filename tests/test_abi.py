@@ -40,7 +40,9 @@ def test_host_only_entry_points():
     assert out.value >= keys_only + (1 << 26) * 4
     assert L.b200alg_radix_sort_temp_bytes(_native.U64, 1 << 28, 4, ctypes.byref(out)) == 0
     assert out.value // 4 < 2 ** 31          # fits the reference's Index1D count of ints
-    assert L.b200alg_radix_sort_temp_bytes(_native.U32, 2 ** 31, 0, ctypes.byref(out)) == _native.TOO_LARGE
+    assert L.b200alg_radix_sort_temp_bytes(_native.U32, 2 ** 31, 0, ctypes.byref(out)) == 0   # 64-bit lengths inside
+    assert out.value >= 2 ** 33
+    assert L.b200alg_radix_sort_temp_bytes(_native.U32, 2 ** 38 + 1, 0, ctypes.byref(out)) == _native.TOO_LARGE
     assert L.b200alg_radix_sort_temp_bytes(99, 10, 0, ctypes.byref(out)) == _native.UNSUPPORTED
     assert L.b200alg_scan_temp_bytes(_native.F32, 1 << 30, ctypes.byref(out)) == 0 and out.value > 0
     assert L.b200alg_scan_temp_bytes(_native.I8, 10, ctypes.byref(out)) == _native.UNSUPPORTED

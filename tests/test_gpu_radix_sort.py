@@ -170,3 +170,44 @@ def test_literal_two_bit_restatement_agrees(accelerator):
     keys = _random_keys("Int32", 1027, 5)
     literal = oracle.radix_sort(keys, literal=True)[0]
     np.testing.assert_array_equal(_sort_keys(accelerator, Ops.AscendingInt32, keys), literal)
+
+
+@pytest.mark.parametrize("key_t,seq_name,np_val", [
+    ("UInt64", "IndexSequencer", np.int32), ("UInt32", "UInt32Sequencer", np.uint32), ("Int32", "Int64Sequencer", np.int64),
+    ("Float", "FloatSequencer", np.float32), ("UInt8", "UInt16Sequencer", np.uint16), ("Int16", "UInt8Sequencer", np.uint8),
+    ("Double", "DoubleSequencer", np.float64), ("UInt16", "HalfSequencer", np.float16)])
+@pytest.mark.parametrize("direction", ["Ascending", "Descending"])
+def test_pairs_with_sequencer_values(accelerator, key_t, seq_name, np_val, direction):
+    """The sequencer overload (RadixSortExtensions.cs:1017-1074): the value of element i is
+    sequencer.ComputeSequenceElement(i) = the index converted to the value type; the value
+    view only receives the result and starts out as garbage here."""
+    import ilgpu_b200 as ib
+    op = getattr(Ops, direction + key_t)
+    seq = getattr(ib.Sequencers, seq_name)
+    for n in [1, 4097, 250_003]:
+        rng = np.random.default_rng(n)
+        keys = rng.integers(0, 50, size=n).astype(NP[key_t])
+        if key_t in ("Int32", "Int16", "Float", "Double"):
+            keys = (keys - 25).astype(NP[key_t])
+        values = np.arange(n).astype(np_val)        # what the sequencer yields (wraps / rounds like the cast)
+        ek, ev = oracle.radix_sort(keys, values, descending=op.descending)
+        dk = to_device(keys)
+        dv = to_device(rng.integers(0, 255, size=n * np.dtype(np_val).itemsize).astype(np.uint8)).view(seq.dtype)
+        temp = accelerator.Allocate1D(accelerator.ComputeRadixSortPairsTempStorageSize(op, dv.dtype, n), torch.int32)
+        accelerator.CreateRadixSortPairs(op, sequencer=ib.Sequencers)(None, dk, dv, seq, temp)
+        accelerator.CheckDeviceStatus(None, temp)
+        np.testing.assert_array_equal(_bits(to_host(dk)), _bits(ek))
+        np.testing.assert_array_equal(_bits(to_host(dv)), _bits(ev))
+
+
+def test_pairs_with_sequencer_when_every_key_is_equal(accelerator):
+    """No digit pass runs (all keys equal): the values still have to be produced."""
+    import ilgpu_b200 as ib
+    n = 100_003
+    dk = to_device(np.full(n, 7, dtype=np.uint32))
+    dv = to_device(np.full(n, 99, dtype=np.int32))
+    op = Ops.AscendingUInt32
+    temp = accelerator.Allocate1D(accelerator.ComputeRadixSortPairsTempStorageSize(op, dv.dtype, n), torch.int32)
+    accelerator.CreateRadixSortPairs(op, sequencer=ib.Sequencers)(None, dk, dv, ib.Sequencers.IndexSequencer, temp)
+    np.testing.assert_array_equal(to_host(dv), np.arange(n, dtype=np.int32))
+    np.testing.assert_array_equal(to_host(dk), np.full(n, 7, dtype=np.uint32))

@@ -2,7 +2,7 @@
 temp view: stream callbacks, allocator-free loops, hosts that forbid cudaMalloc after
 start-up) must give exactly what the regular entry point gives.  Both are called through
 the C ABI, twice in a row, because the second call finds the first one's leftovers in the
-shared scratch array.  Collected last on purpose (file name), and self-contained so that
+shared scratch array; integer results are also held against the CPU oracle.  Collected last on purpose (file name), and self-contained so that
 it also passes alone in a fresh process."""
 import ctypes
 
@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from ilgpu_b200 import _native as N
+from oracle import cpu_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -58,6 +59,12 @@ def test_static_scratch_scan_matches_regular_scan_twice_in_a_row():
         else:
             assert torch.equal(first, expected)
             assert torch.equal(second, expected)
+            # and both equal what the reference's CPU path computes (integers: bit-exact)
+            want = oracle.scan(host, {N.ADD: "add", N.MAX: "max", N.MIN: "min"}[op], bool(inclusive))
+            np.testing.assert_array_equal(second.cpu().numpy(), want)
+        # a bounded wait that ran out inside the built-in scratch would show here (temp = NULL
+        # asks about that array)
+        assert L.b200alg_device_status(stream, None) == N.OK
 
 
 def test_static_scratch_scan_rejects_sizes_beyond_its_limit():
