@@ -478,9 +478,14 @@ def run_native(args) -> None:
         last = [None]
 
         def step_fn(i):
-            last[0] = sharded.SortKeys(bufs[i], op)   # the previous step's output goes back to the allocator
+            # enqueued without a host synchronisation; the previous step's output goes back to the allocator
+            last[0] = sharded.SortAsync(bufs[i], None, op)
         launches_per_step = sharded.sort_launches_per_step(op)
-        result_of = lambda i: last[0][0]
+
+        def result_of(i):
+            out, _, count = last[0]
+            sharded.CheckStatus()
+            return out[: int(count.item())]
 
     sampler = ClockSampler(local_rank)
     sampler.start()          # nvidia-smi takes a moment to start: launch it before the warm-up
@@ -620,7 +625,7 @@ def run_native(args) -> None:
         "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": {
             "workload": "RadixSort ascending, 2^26 uint32 keys per GPU, i.i.d. uniform over the full range (seeded), "
-                        "4 digit passes of 8 bits" + ("" if world == 1 else "; sample sort across GPUs, buckets exchanged by peer stores from the partition kernel"),
+                        "4 digit passes of 8 bits" + ("" if world == 1 else "; sample sort across GPUs inside the native multi-GPU library, buckets exchanged by peer stores from the partition kernel, no host synchronisation"),
             "keys_per_gpu": n, "total_keys": world * n,
             "l2": "inputs larger than L2: 256 MiB per step, a fresh unsorted buffer each step",
         },

@@ -33,6 +33,7 @@ SIGNATURES = {
     "b200alg_radix_sort_keys": (_int, [_vp, _vp, _i64, _i64, _int, _int, _vp, _i64]),
     "b200alg_radix_sort_pairs": (_int, [_vp, _vp, _vp, _i64, _int, _int, _int, _vp, _i64]),
     "b200alg_radix_sort_pairs_sequence": (_int, [_vp, _vp, _vp, _i64, _int, _int, _int, _vp, _i64]),
+    "b200alg_radix_sort_out_of_place": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _int, _int, _int, _vp, _i64]),
     "b200alg_bucket_partition_temp_bytes": (_int, [_int, _i64, ctypes.POINTER(_i64)]),
     "b200alg_bucket_partition": (_int, [_vp, _vp, _vp, _i64, _int, _int, _int, _vp, _vp, _int, _i64, _vp, _vp, _vp, _vp, _i64]),
     "b200alg_bucket_count": (_int, [_vp, _vp, _i64, _int, _int, _vp, _vp, _int, _i64, _vp, _vp, _i64]),
@@ -50,11 +51,48 @@ SIGNATURES = {
     "b200alg_device_status": (_int, [_vp, _vp]),
 }
 
+# multi-GPU layer (include/b200alg_mg.h): libb200alg_mg.so, loaded on first use
+MG_LIB_PATH = os.environ.get("B200ALG_MG_LIBRARY") or os.path.join(_HERE, "libb200alg_mg.so")
+NCCL_ERROR = 9
+UNIQUE_ID_BYTES = 128
+_pp = ctypes.POINTER(ctypes.c_void_p)
+MG_SIGNATURES = {
+    "b200alg_comm_unique_id": (_int, [_vp]),
+    "b200alg_comm_create_rank": (_int, [_vp, _int, _int, _i64, _pp]),
+    "b200alg_comm_create": (_int, [_int, ctypes.POINTER(_int), _i64, _pp]),
+    "b200alg_comm_destroy": (_int, [_vp]),
+    "b200alg_comm_rank": (_int, [_vp, ctypes.POINTER(_int), ctypes.POINTER(_int)]),
+    "b200alg_comm_status": (_int, [_vp, _vp]),
+    "b200alg_comm_last_nccl_error": (_int, [_vp]),
+    "b200alg_reduce_mg": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _vp]),
+    "b200alg_histogram_mg": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _dbl, _dbl, _vp, _i64, _int, _vp]),
+    "b200alg_scan_mg": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _int, _int, _vp, _i64]),
+    "b200alg_sort_mg": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _int, _int, _vp, _vp, _i64, _vp]),
+}
+
 _lib = None
+_mg_lib = None
 
 
 class NativeLibraryMissing(RuntimeError):
     pass
+
+
+def mg_lib() -> ctypes.CDLL:
+    """Loads the multi-GPU library once (it needs NCCL and libb200alg.so); raises
+    NativeLibraryMissing when it is not built."""
+    global _mg_lib
+    if _mg_lib is None:
+        lib()  # the single-GPU library first: the multi-GPU one links against it
+        if not os.path.exists(MG_LIB_PATH):
+            raise NativeLibraryMissing(f"{MG_LIB_PATH} not found; build it with `make -C ilgpu_b200/csrc`")
+        L = ctypes.CDLL(MG_LIB_PATH)
+        for name, (res, args) in MG_SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _mg_lib = L
+    return _mg_lib
 
 
 def lib() -> ctypes.CDLL:
@@ -65,7 +103,7 @@ def lib() -> ctypes.CDLL:
             raise NativeLibraryMissing(
                 f"{LIB_PATH} not found: the CUDA library is required (there is no CPU or "
                 "PyTorch fallback); build it with `make -C ilgpu_b200/csrc`")
-        L = ctypes.CDLL(LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(L, name)  # AttributeError if the export is missing
             fn.restype = res

@@ -84,6 +84,7 @@ extern "C" const char *b200alg_status_string(int status) {
     case B200ALG_MISALIGNED: return "pointer not aligned";
     case B200ALG_TOO_LARGE: return "more elements than the library indexes (2^38)";
     case B200ALG_STATIC_LIMIT: return "more elements than the built-in scratch of this entry point covers";
+    case B200ALG_NCCL_ERROR: return "NCCL error (see b200alg_comm_last_nccl_error)";
     }
     return "unknown status";
 }

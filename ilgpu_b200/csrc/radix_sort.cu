@@ -26,10 +26,31 @@ constexpr int kMaxPasses = 8;
 enum : int {
     kCtlTicket = 0,        // [0..7]  next tile of each pass (tiles are handed out in order)
     kCtlSkip = 8,          // [8..15] 1 = every key has the same digit at this position
-    kCtlSrcIsAlt = 16,     // [16..23] 1 = this pass reads the alternate buffer
-    kCtlFinalInAlt = 24,   // 1 = the sorted data ended in the alternate buffer
-    kCtlFirstPass = 25     // first pass that runs (kNoPass when every pass is skipped)
+    kCtlSrc = 16,          // [16..23] buffer this pass reads (kBufIn / kBufOut / kBufAlt)
+    kCtlFinal = 24,        // buffer the sorted data ended in (kBufOut: nothing left to do)
+    kCtlFirstPass = 25,    // first pass that runs (kNoPass when every pass is skipped)
+    kCtlDst = 32,          // [32..39] buffer this pass writes
+    kCtlStatusHalf = 40    // [40..47] which of the two look-back arrays this pass uses
 };
+// The three buffers a sort moves its data between.
+enum : unsigned int { kBufIn = 0, kBufOut = 1, kBufAlt = 2 };
+
+// Views of one sort call.  An in-place sort has in == out (possibly strided); an out-of-place
+// sort leaves `in` untouched.  The alternate buffer is dense scratch of n elements.
+template <typename K, typename V> struct SortBuffers {
+    const K *in;
+    K *out, *alt;
+    const V *vin;
+    V *vout, *valt;
+    int64_t stride;             // of the input / output view
+    int64_t n;                  // element count, or its upper bound when n_device is set
+    const long long *n_device;  // element count in device memory (NULL: n is exact)
+};
+template <typename K, typename V> __device__ __forceinline__ int64_t effective_n(const SortBuffers<K, V> &io) {
+    if (!io.n_device) return io.n;
+    const long long v = *io.n_device;
+    return v < 0 ? 0 : (v > io.n ? io.n : (int64_t)v);
+}
 constexpr unsigned int kNoPass = 0xFFu;
 
 // Values that are a function of the element's index (the reference's sequencers:
@@ -99,8 +120,13 @@ constexpr int kHistoMaxSmem = 128 * 1024;
 
 template <typename K, int RSHIFT>
 __global__ void __launch_bounds__(kHistoThreads)
-sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, KeyXform<K> xf, unsigned long long *ghist) {
+sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, const long long *n_device, KeyXform<K> xf,
+                      unsigned long long *ghist) {
     constexpr int P = sizeof(K);
+    if (n_device) {
+        const long long v = *n_device;
+        n = v < 0 ? 0 : (v > n ? n : (int64_t)v);
+    }
     constexpr int rshift = RSHIFT;
     // replicas are interleaved ([position][digit][replica]) so that the lanes of a warp spread
     // over the banks even when their digits collide
@@ -157,18 +183,25 @@ sort_histogram_kernel(const K *__restrict__ keys, int64_t stride, int64_t n, Key
 }
 
 // ---- 2. global digit offsets, skipped passes, buffer schedule ---------------------------
+// skip_enabled: a pass on whose digit every key agrees does not run.  out_of_place: the input
+// view is only read; the passes then alternate between the output view and the alternate
+// buffer so that the last one writes the output view.  In place, they alternate between the
+// view and the alternate buffer, and the result is copied home if it ended in the latter.
 __global__ void __launch_bounds__(kRadix)
-sort_offsets_kernel(const unsigned long long *ghist, unsigned long long *gbase, TempHeader *hdr, int passes, unsigned long long n) {
+sort_offsets_kernel(const unsigned long long *ghist, unsigned long long *gbase, TempHeader *hdr, int passes, long long n,
+                    const long long *n_device, int skip_enabled, int out_of_place) {
     __shared__ unsigned long long warp_sum[kRadix / 32];
     __shared__ int s_skip;
     const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
-    int src_is_alt = 0;
-    unsigned int first = kNoPass;
+    if (n_device) {
+        const long long v = *n_device;
+        n = v < 0 ? 0 : (v > n ? n : v);
+    }
     for (int p = 0; p < passes; ++p) {
         if (d == 0) s_skip = 0;
         __syncthreads();
         const unsigned long long c = ghist[p * kRadix + d];
-        if (c == n) s_skip = 1;
+        if (skip_enabled && c == (unsigned long long)n) s_skip = 1;
         unsigned long long incl = c;
 #pragma unroll
         for (int k = 1; k < 32; k <<= 1) {
@@ -180,17 +213,27 @@ sort_offsets_kernel(const unsigned long long *ghist, unsigned long long *gbase, 
         unsigned long long before = 0;
         for (int w = 0; w < warp; ++w) before += warp_sum[w];
         gbase[p * kRadix + d] = before + incl - c;
-        const int skip = s_skip;
-        if (d == 0) {
-            hdr->reserved[kCtlSkip + p] = (unsigned)skip;
-            hdr->reserved[kCtlSrcIsAlt + p] = (unsigned)src_is_alt;
-        }
-        if (!skip && d == 0 && first == kNoPass) first = (unsigned)p;
-        if (!skip) src_is_alt ^= 1;
+        if (d == 0) hdr->reserved[kCtlSkip + p] = (unsigned)s_skip;
         __syncthreads();
     }
     if (d == 0) {
-        hdr->reserved[kCtlFinalInAlt] = (unsigned)src_is_alt;
+        int running = 0;
+        for (int p = 0; p < passes; ++p) running += hdr->reserved[kCtlSkip + p] ? 0 : 1;
+        unsigned int first = kNoPass, cur = out_of_place ? kBufIn : kBufOut;
+        int j = 0;
+        for (int p = 0; p < passes; ++p) {
+            if (hdr->reserved[kCtlSkip + p]) continue;
+            if (first == kNoPass) first = (unsigned)p;
+            unsigned int dst;
+            if (out_of_place) dst = ((running - 1 - j) & 1) ? kBufAlt : kBufOut;
+            else dst = cur == kBufOut ? kBufAlt : kBufOut;
+            hdr->reserved[kCtlSrc + p] = cur;
+            hdr->reserved[kCtlDst + p] = dst;
+            hdr->reserved[kCtlStatusHalf + p] = (unsigned)(j & 1);
+            cur = dst;
+            ++j;
+        }
+        hdr->reserved[kCtlFinal] = cur;
         hdr->reserved[kCtlFirstPass] = first;
     }
 }
@@ -293,17 +336,29 @@ struct OnesweepSmem {
     // [sorted: the reorder buffer][counts per warp and digit][lane masks per warp and digit]
     // [digit's first slot in the tile, digit's count][digit's global offset][small words +
     // mbarrier][pass description][digit of every slot][splitters][staged keys]
+    // The lane masks are only alive while a tile is ranked, the reorder buffer only afterwards:
+    // when two blocks per SM would not fit otherwise, the masks live at the head of the
+    // reorder buffer (and every warp clears its row again before it ranks the next tile).
+    static constexpr size_t table_bytes = (size_t)WARPS * kRadix * 4;
+    static constexpr size_t fixed_bytes = kRadix * 16 + 256 + (KEEP_DIGITS ? (size_t)TILE + kRadix * 16 : 0) + 128;
+    static constexpr bool MASKS_IN_SORTED =
+        (size_t)TILE * SLOT >= table_bytes &&
+        (size_t)TILE * SLOT + 2 * table_bytes + fixed_bytes + (size_t)TILE * sizeof(K) > 112 * 1024;
     static constexpr size_t off_sorted = 0;
     static constexpr size_t off_count = (size_t)TILE * SLOT;
-    static constexpr size_t off_mask = off_count + (size_t)WARPS * kRadix * 4;
-    static constexpr size_t off_excl = off_mask + (size_t)WARPS * kRadix * 4;
+    static constexpr size_t off_mask = MASKS_IN_SORTED ? off_sorted : off_count + table_bytes;
+    static constexpr size_t off_excl = off_count + table_bytes + (MASKS_IN_SORTED ? 0 : table_bytes);
     static constexpr size_t off_goff = off_excl + kRadix * 8;
     static constexpr size_t off_misc = off_goff + kRadix * 8;
     static constexpr size_t off_context = off_misc + 128;   // the block's PassContext
     static constexpr size_t off_digits = off_context + 128;
     static constexpr size_t off_splitters = off_digits + (KEEP_DIGITS ? (size_t)TILE : 0);
     static constexpr size_t off_stage = (off_splitters + (KEEP_DIGITS ? (size_t)kRadix * 16 : 0) + 127) / 128 * 128;
-    static constexpr size_t bytes = off_stage + (kSortTma ? (size_t)TILE * sizeof(K) : 0);
+    // The staging buffer of the bulk copies is dropped (keys are then loaded directly) where
+    // it would cost the second block per SM.
+    static constexpr size_t kTwoBlocksPerSm = 113 * 1024;
+    static constexpr bool STAGED = kSortTma && (THREADS > 512 || off_stage + (size_t)TILE * sizeof(K) <= kTwoBlocksPerSm);
+    static constexpr size_t bytes = off_stage + (STAGED ? (size_t)TILE * sizeof(K) : 0);
 };
 
 // Everything one block needs to know about the pass it works on.
@@ -327,10 +382,10 @@ template <typename K, typename V, typename SW> struct PassContext {
 // Hands out the block's next tile and, when that tile is a full one of a bulk-copyable
 // source, starts the copy of its keys into the staging buffer.  One thread calls this once
 // every thread of the block has taken the current tile's keys out of the staging buffer.
-template <typename K, typename V, typename SW, int TILE>
+template <typename K, typename V, typename SW, int TILE, bool STAGED>
 __device__ __forceinline__ int take_ticket(const PassContext<K, V, SW> &c, K *stage, unsigned long long *bar) {
     const int next = (int)atomicAdd(c.ticket, 1u);
-    if (kSortTma && c.bulk && next < c.num_tiles && (int64_t)(next + 1) * TILE <= c.n) {
+    if (STAGED && c.bulk && next < c.num_tiles && (int64_t)(next + 1) * TILE <= c.n) {
         mbar_expect_tx(bar, (unsigned int)(TILE * sizeof(K)));
         bulk_load(stage, c.src + (int64_t)next * TILE, (unsigned int)(TILE * sizeof(K)), bar);
     }
@@ -371,15 +426,19 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
     unsigned int *my_mask = mask_tbl + warp * kRadix;
 
     // The warp's own row of the count table starts at zero (nobody else touches it before the
-    // first block-wide barrier of the tile); its lane masks are left at zero by every item.
+    // first block-wide barrier of the tile); its lane masks are left at zero by every item
+    // unless they share their memory with the reorder buffer.
     {
-        uint4 *zc = reinterpret_cast<uint4 *>(my_count);
+        uint4 *zc = reinterpret_cast<uint4 *>(my_count), *zm = reinterpret_cast<uint4 *>(my_mask);
 #pragma unroll
-        for (int i = 0; i < kRadix / 4 / 32; ++i) zc[i * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
+        for (int i = 0; i < kRadix / 4 / 32; ++i) {
+            zc[i * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
+            if (L::MASKS_IN_SORTED) zm[i * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);  // the reorder buffer's leftovers
+        }
     }
 
     K key[ITEMS];
-    if (FAST && kSortTma && c.bulk) {
+    if (FAST && L::STAGED && c.bulk) {
         if (!mbar_wait(bar, bulk_phase) && lane == 0) atomicExch(&c.hdr->wait_limit_hit, 1u);
         bulk_phase ^= 1u;
 #pragma unroll
@@ -448,7 +507,7 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
     }
     __syncthreads();  // A: the tables are complete; every thread has its keys out of the staging buffer
 
-    if (tid == THREADS - 1) misc[8] = (unsigned int)take_ticket<K, V, SW, TILE>(c, stage, bar);
+    if (tid == THREADS - 1) misc[8] = (unsigned int)take_ticket<K, V, SW, TILE, L::STAGED>(c, stage, bar);
 
     // The first 256 threads (one per digit) turn the warps' digit counts into slots of the
     // reorder buffer and publish the tile's counts for the tiles behind it.
@@ -606,8 +665,8 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
 // blocks of the grid are resident.
 template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS)
-onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, int pass, Digit dg,
-                TempHeader *hdr, const unsigned long long *gbase_all, SW *status_all, int num_tiles, int value_seq) {
+onesweep_kernel(SortBuffers<K, V> io, int pass, Digit dg, TempHeader *hdr, const unsigned long long *gbase_all,
+                SW *status_all, int max_tiles, int value_seq) {
     constexpr int TILE = THREADS * ITEMS;
     static_assert(THREADS >= 2 * kRadix, "one thread per digit for the offsets and one for the look-back");
     using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
@@ -619,18 +678,19 @@ onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, 
     static_assert(sizeof(PassContext<K, V, SW>) <= 128, "context slot");
     PassContext<K, V, SW> &c = *reinterpret_cast<PassContext<K, V, SW> *>(smem_raw + L::off_context);
     unsigned int *misc = reinterpret_cast<unsigned int *>(smem_raw + L::off_misc);
+    const int64_t n = effective_n(io);
+    const int num_tiles = (int)((n + TILE - 1) / TILE);
     if (threadIdx.x == THREADS - 1) {
-        const bool src_is_alt = hdr->reserved[kCtlSrcIsAlt + pass] != 0;
-        // Buffer 0 is the caller's (possibly strided) view, buffer 1 the dense alternate.
-        c.src = src_is_alt ? buf1 : buf0;
-        c.dst = src_is_alt ? buf0 : buf1;
-        c.src_stride = src_is_alt ? 1 : stride0;
-        c.dst_stride = src_is_alt ? stride0 : 1;
-        c.vsrc = src_is_alt ? val1 : val0;
-        c.vdst = src_is_alt ? val0 : val1;
+        const unsigned int src = hdr->reserved[kCtlSrc + pass], dst = hdr->reserved[kCtlDst + pass];
+        c.src = src == kBufIn ? io.in : (src == kBufOut ? io.out : io.alt);
+        c.dst = dst == kBufOut ? io.out : io.alt;
+        c.src_stride = src == kBufAlt ? 1 : io.stride;
+        c.dst_stride = dst == kBufAlt ? 1 : io.stride;
+        c.vsrc = src == kBufIn ? io.vin : (src == kBufOut ? io.vout : io.valt);
+        c.vdst = dst == kBufOut ? io.vout : io.valt;
         c.n = n;
         c.num_tiles = num_tiles;
-        c.dense = stride0 == 1;
+        c.dense = io.stride == 1;
         c.bulk = c.dense && ((uintptr_t)c.src % 16 == 0);
         c.value_seq = hdr->reserved[kCtlFirstPass] == (unsigned int)pass ? value_seq : kSeqNone;
         c.hdr = hdr;
@@ -638,22 +698,27 @@ onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, 
         c.gbase = gbase_all + pass * kRadix;
         // Two look-back arrays alternate between the passes that run; this pass clears the
         // slots the next one will use (the previous pass, their last user, has completed).
-        c.status = status_all + (src_is_alt ? (size_t)num_tiles * kRadix : 0);
-        c.status_next = status_all + (src_is_alt ? 0 : (size_t)num_tiles * kRadix);
+        const bool upper = hdr->reserved[kCtlStatusHalf + pass] != 0;
+        c.status = status_all + (upper ? (size_t)max_tiles * kRadix : 0);
+        c.status_next = status_all + (upper ? 0 : (size_t)max_tiles * kRadix);
         unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + L::off_misc + 64);
-        if (kSortTma) {
+        if (L::STAGED) {
             mbar_init(bar, 1u);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
-        misc[8] = (unsigned int)take_ticket<K, V, SW, TILE>(c, reinterpret_cast<K *>(smem_raw + L::off_stage), bar);
+        misc[8] = (unsigned int)take_ticket<K, V, SW, TILE, L::STAGED>(c, reinterpret_cast<K *>(smem_raw + L::off_stage), bar);
     }
     if constexpr (Digit::kUsesIndex)
         dg.stage(reinterpret_cast<K *>(smem_raw + L::off_splitters + kRadix * 8),
                  reinterpret_cast<int64_t *>(smem_raw + L::off_splitters));
+    {   // the lane masks of the ranking tables start at zero and are left at zero by every item
+        uint4 *zm = reinterpret_cast<uint4 *>(smem_raw + L::off_mask);
+        for (int i = threadIdx.x; i < (THREADS / 32) * kRadix / 4; i += THREADS) zm[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
     __syncthreads();
     int tile = (int)misc[8];
     __syncthreads();  // misc[8] is written again during the first tile
-    const bool dense = stride0 == 1;
+    const bool dense = io.stride == 1;
     unsigned int bulk_phase = 0u;
     while (tile < num_tiles) {
         if (dense && (int64_t)(tile + 1) * TILE <= n)
@@ -663,21 +728,32 @@ onesweep_kernel(K *buf0, int64_t stride0, K *buf1, V *val0, V *val1, int64_t n, 
     }
 }
 
-// ---- 4. bring the result home when it ended in the alternate buffer ---------------------
+// ---- 4. bring the result home when it did not end in the output view ---------------------
 template <typename K, typename V>
 __global__ void __launch_bounds__(256)
-sort_copy_back_kernel(K *buf0, int64_t stride0, const K *buf1, V *val0, const V *val1, int64_t n, const TempHeader *hdr,
-                      int value_seq) {
+sort_copy_back_kernel(SortBuffers<K, V> io, const TempHeader *hdr, int value_seq) {
+    const int64_t n = effective_n(io);
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned int final_in = hdr->reserved[kCtlFinal];
+    bool values_made = false;
     if constexpr (ValueBytes<V>::value != 0 && sizeof(V) <= 8) {
-        // no pass ran (every key equal): the keys stay where they are, the values still have to be made
-        if (value_seq != kSeqNone && hdr->reserved[kCtlFirstPass] == kNoPass)
-            for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) val0[i] = sequence_value<V>(value_seq, i);
+        // no pass ran (every key equal): the keys stay in order, the values still have to be made
+        if (value_seq != kSeqNone && hdr->reserved[kCtlFirstPass] == kNoPass) {
+            for (int64_t i = first; i < n; i += step) io.vout[i] = sequence_value<V>(value_seq, i);
+            values_made = true;
+        }
     }
-    if (!hdr->reserved[kCtlFinalInAlt]) return;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
-        buf0[i * stride0] = buf1[i];
-        if constexpr (ValueBytes<V>::value != 0) val0[i] = val1[i];
+    if (final_in == kBufOut) return;
+    if (final_in == kBufIn && (const void *)io.in == (const void *)io.out) return;
+    const K *from = final_in == kBufAlt ? io.alt : io.in;
+    const V *vfrom = final_in == kBufAlt ? io.valt : io.vin;
+    const int64_t from_stride = final_in == kBufAlt ? 1 : io.stride;
+    for (int64_t i = first; i < n; i += step) {
+        io.out[i * io.stride] = from[i * from_stride];
+        if constexpr (ValueBytes<V>::value != 0) {
+            if (!values_made) io.vout[i] = vfrom[i];
+        }
     }
 }
 
@@ -736,9 +812,21 @@ static int configure_persistent(KernelT kernel, int threads, size_t bytes, int *
     return B200ALG_OK;
 }
 
+// What a sort call works on, untyped (the entry points fill this in).
+struct SortCall {
+    const void *in_keys;
+    void *out_keys;
+    const void *in_values;
+    void *out_values;
+    int64_t stride;
+    int64_t n;                  // element count, or its upper bound when n_device is set
+    const long long *n_device;
+    int value_seq;
+    bool out_of_place;
+};
+
 template <typename K, typename V, typename SW, typename XF>
-static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_t n, const KeyXform<K> &xf, void *temp,
-                      const SortLayout &L, int value_seq) {
+static int run_passes(cudaStream_t s, const SortCall &call, const KeyXform<K> &xf, void *temp, const SortLayout &L) {
     constexpr int THREADS = SortTuning<K>::THREADS, ITEMS = SortTuning<K>::ITEMS;
     using Smem = OnesweepSmem<K, V, false, THREADS, ITEMS>;
     auto kernel = onesweep_kernel<K, V, SW, RadixDigit<K, XF>, THREADS, ITEMS>;
@@ -747,6 +835,7 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
         const int rc = configure_persistent(kernel, THREADS, Smem::bytes, &blocks_per_sm);
         if (rc != B200ALG_OK) return rc;
     }
+    const int64_t n = call.n;
     const int64_t resident = (int64_t)sm_count() * blocks_per_sm;
     const int grid = (int)(L.tiles < resident ? L.tiles : resident);
     char *t = (char *)temp;
@@ -754,8 +843,16 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
     unsigned long long *ghist = (unsigned long long *)(t + L.off_ghist);
     unsigned long long *gbase = (unsigned long long *)(t + L.off_gbase);
     SW *status = (SW *)(t + L.off_status);
-    K *alt_keys = (K *)(t + L.off_keys);
-    V *alt_vals = (V *)(t + L.off_values);
+    SortBuffers<K, V> io;
+    io.in = (const K *)call.in_keys;
+    io.out = (K *)call.out_keys;
+    io.alt = (K *)(t + L.off_keys);
+    io.vin = (const V *)call.in_values;
+    io.vout = (V *)call.out_values;
+    io.valt = (V *)(t + L.off_values);
+    io.stride = call.stride;
+    io.n = n;
+    io.n_device = call.n_device;
 
     B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)L.control_bytes, s));
     {
@@ -777,52 +874,50 @@ static int run_passes(cudaStream_t s, K *keys, int64_t stride, V *values, int64_
             }
         }
         if (big)
-            sort_histogram_kernel<K, kBigShift><<<blocks, kHistoThreads, histo_smem, s>>>(keys, stride, n, xf, ghist);
+            sort_histogram_kernel<K, kBigShift><<<blocks, kHistoThreads, histo_smem, s>>>(io.in, io.stride, n, io.n_device, xf, ghist);
         else
-            sort_histogram_kernel<K, 3><<<blocks, kHistoThreads, histo_smem, s>>>(keys, stride, n, xf, ghist);
+            sort_histogram_kernel<K, 3><<<blocks, kHistoThreads, histo_smem, s>>>(io.in, io.stride, n, io.n_device, xf, ghist);
         B200ALG_LAUNCH_CHECK();
     }
-    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, L.passes, (unsigned long long)n);
+    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, L.passes, (long long)n, io.n_device, 1, call.out_of_place ? 1 : 0);
     B200ALG_LAUNCH_CHECK();
     for (int p = 0; p < L.passes; ++p) {
         RadixDigit<K, XF> dg;
         if constexpr (std::is_same<XF, KeyXform<K>>::value) dg.xf = xf;
         dg.shift = p * 8;
-        kernel<<<grid, THREADS, Smem::bytes, s>>>(keys, stride, alt_keys, values, alt_vals, n, p, dg, hdr, gbase, status,
-                                                  (int)L.tiles, value_seq);
+        kernel<<<grid, THREADS, Smem::bytes, s>>>(io, p, dg, hdr, gbase, status, (int)L.tiles, call.value_seq);
         B200ALG_LAUNCH_CHECK();
     }
     {
         int64_t want = ceil_div(n, 256 * 8);
         const int64_t cap = (int64_t)sm_count() * 8;
         const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-        sort_copy_back_kernel<K, V><<<blocks, 256, 0, s>>>(keys, stride, alt_keys, values, alt_vals, n, hdr, value_seq);
+        sort_copy_back_kernel<K, V><<<blocks, 256, 0, s>>>(io, hdr, call.value_seq);
         B200ALG_LAUNCH_CHECK();
     }
     return B200ALG_OK;
 }
 
 template <typename K, typename V>
-static int run_sort(cudaStream_t s, void *keys, int64_t stride, void *values, int64_t n, uint64_t xn, uint64_t xp,
-                    void *temp, const SortLayout &L, int value_seq) {
+static int run_sort(cudaStream_t s, const SortCall &call, uint64_t xn, uint64_t xp, void *temp, const SortLayout &L) {
     KeyXform<K> xf{(K)xn, (K)xp};
     const bool identity = xn == 0 && xp == 0;
     if (L.wide_status) {
-        if (identity) return run_passes<K, V, unsigned long long, KeyIdentity<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L, value_seq);
-        return run_passes<K, V, unsigned long long, KeyXform<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L, value_seq);
+        if (identity) return run_passes<K, V, unsigned long long, KeyIdentity<K>>(s, call, xf, temp, L);
+        return run_passes<K, V, unsigned long long, KeyXform<K>>(s, call, xf, temp, L);
     }
-    if (identity) return run_passes<K, V, unsigned int, KeyIdentity<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L, value_seq);
-    return run_passes<K, V, unsigned int, KeyXform<K>>(s, (K *)keys, stride, (V *)values, n, xf, temp, L, value_seq);
+    if (identity) return run_passes<K, V, unsigned int, KeyIdentity<K>>(s, call, xf, temp, L);
+    return run_passes<K, V, unsigned int, KeyXform<K>>(s, call, xf, temp, L);
 }
 
 template <typename V>
-static int dispatch_key(cudaStream_t s, int key_bytes, void *keys, int64_t stride, void *values, int64_t n, uint64_t xn,
-                        uint64_t xp, void *temp, const SortLayout &L, int value_seq) {
+static int dispatch_key(cudaStream_t s, int key_bytes, const SortCall &call, uint64_t xn, uint64_t xp, void *temp,
+                        const SortLayout &L) {
     switch (key_bytes) {
-    case 1: return run_sort<uint8_t, V>(s, keys, stride, values, n, xn, xp, temp, L, value_seq);
-    case 2: return run_sort<uint16_t, V>(s, keys, stride, values, n, xn, xp, temp, L, value_seq);
-    case 4: return run_sort<uint32_t, V>(s, keys, stride, values, n, xn, xp, temp, L, value_seq);
-    case 8: return run_sort<uint64_t, V>(s, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 1: return run_sort<uint8_t, V>(s, call, xn, xp, temp, L);
+    case 2: return run_sort<uint16_t, V>(s, call, xn, xp, temp, L);
+    case 4: return run_sort<uint32_t, V>(s, call, xn, xp, temp, L);
+    case 8: return run_sort<uint64_t, V>(s, call, xn, xp, temp, L);
     }
     return B200ALG_UNSUPPORTED;
 }
@@ -937,12 +1032,12 @@ static int run_partition(cudaStream_t s, const K *keys, const V *values, int64_t
     }
     // One "pass": offsets of the buckets; the skip rule is off (n + 1 never matches a count),
     // so the pass always moves the keys from buffer 0 (input) to buffer 1 (output).
-    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (unsigned long long)n + 1ull);
+    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (long long)n, nullptr, 0, 1);
     B200ALG_LAUNCH_CHECK();
     export_bucket_counts_kernel<<<1, kRadix, 0, s>>>(ghist, counts, num_buckets);
     B200ALG_LAUNCH_CHECK();
-    kernel<<<grid, THREADS, Smem::bytes, s>>>(const_cast<K *>(keys), 1, out_keys, const_cast<V *>(values), out_values, n, 0,
-                                              dg, hdr, gbase, status, (int)L.tiles, (int)kSeqNone);
+    SortBuffers<K, V> io{keys, out_keys, nullptr, values, out_values, nullptr, 1, n, nullptr};
+    kernel<<<grid, THREADS, Smem::bytes, s>>>(io, 0, dg, hdr, gbase, status, (int)L.tiles, (int)kSeqNone);
     B200ALG_LAUNCH_CHECK();
     return B200ALG_OK;
 }
@@ -985,10 +1080,10 @@ static int run_bucket_scatter(cudaStream_t s, const K *keys, const V *values, in
     B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)L.control_bytes, s));
     // all-zero histogram: the bucket offsets come out zero (every bucket has its own base
     // pointer) and the pass is scheduled from buffer 0
-    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (unsigned long long)n + 1ull);
+    sort_offsets_kernel<<<1, kRadix, 0, s>>>(ghist, gbase, hdr, 1, (long long)n, nullptr, 0, 1);
     B200ALG_LAUNCH_CHECK();
-    kernel<<<grid, THREADS, Smem::bytes, s>>>(const_cast<K *>(keys), 1, nullptr, const_cast<V *>(values), nullptr, n, 0, dg, hdr,
-                                              gbase, status, (int)L.tiles, (int)kSeqNone);
+    SortBuffers<K, V> io{keys, nullptr, nullptr, values, nullptr, nullptr, 1, n, nullptr};
+    kernel<<<grid, THREADS, Smem::bytes, s>>>(io, 0, dg, hdr, gbase, status, (int)L.tiles, (int)kSeqNone);
     B200ALG_LAUNCH_CHECK();
     return B200ALG_OK;
 }
@@ -1071,31 +1166,35 @@ static int partition_key(cudaStream_t s, int kb, const void *keys, const void *v
     return B200ALG_UNSUPPORTED;
 }
 
-static int sort_common(void *stream, void *keys, int64_t stride, void *values, int64_t n, int key_dtype, int value_bytes,
-                       int order, void *temp, int64_t temp_bytes, int value_seq = kSeqNone) {
+static int sort_common(void *stream, const SortCall &call, int key_dtype, int value_bytes, int order, void *temp,
+                       int64_t temp_bytes) {
     // Argument checks mirror VerifyArguments (RadixSortExtensions.cs:1340-1367).
-    if (!keys || !temp || (value_bytes && !values)) return B200ALG_INVALID_ARGUMENT;
-    if (n < 0 || stride < 1) return B200ALG_INVALID_ARGUMENT;
+    if (!call.in_keys || !call.out_keys || !temp || (value_bytes && !call.out_values)) return B200ALG_INVALID_ARGUMENT;
+    if (value_bytes && !call.in_values && call.value_seq == kSeqNone) return B200ALG_INVALID_ARGUMENT;
+    if (call.n < 0 || call.stride < 1) return B200ALG_INVALID_ARGUMENT;
     const int kb = dtype_bytes(key_dtype);
     if (kb == 0) return B200ALG_UNSUPPORTED;
     if (value_bytes != 0 && value_bytes != 1 && value_bytes != 2 && value_bytes != 4 && value_bytes != 8 && value_bytes != 16)
         return B200ALG_UNSUPPORTED;
-    if (n > kMaxElements) return B200ALG_TOO_LARGE;
-    if (((uintptr_t)keys % kb) || (value_bytes && ((uintptr_t)values % value_bytes)) || ((uintptr_t)temp % 256))
+    if (call.value_seq != kSeqNone && value_bytes == 16) return B200ALG_UNSUPPORTED;
+    if (call.n > kMaxElements) return B200ALG_TOO_LARGE;
+    if (((uintptr_t)call.in_keys % kb) || ((uintptr_t)call.out_keys % kb) || ((uintptr_t)temp % 256)) return B200ALG_MISALIGNED;
+    if (value_bytes && (((uintptr_t)call.in_values % value_bytes) || ((uintptr_t)call.out_values % value_bytes)))
         return B200ALG_MISALIGNED;
+    if (call.n_device && ((uintptr_t)call.n_device % 8)) return B200ALG_MISALIGNED;
     uint64_t xn, xp;
     if (!key_xform_constants(key_dtype, order, xn, xp)) return B200ALG_UNSUPPORTED;
-    const SortLayout L = sort_layout(kb, value_bytes, n);
+    const SortLayout L = sort_layout(kb, value_bytes, call.n);
     if (temp_bytes < L.total) return B200ALG_TEMP_TOO_SMALL;
-    if (n == 0) return B200ALG_OK;
+    if (call.n == 0) return B200ALG_OK;
     cudaStream_t s = (cudaStream_t)stream;
     switch (value_bytes) {
-    case 0: return dispatch_key<NoValue>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
-    case 1: return dispatch_key<uint8_t>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
-    case 2: return dispatch_key<uint16_t>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
-    case 4: return dispatch_key<uint32_t>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
-    case 8: return dispatch_key<uint64_t>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
-    case 16: return dispatch_key<uint4>(s, kb, keys, stride, values, n, xn, xp, temp, L, value_seq);
+    case 0: return dispatch_key<NoValue>(s, kb, call, xn, xp, temp, L);
+    case 1: return dispatch_key<uint8_t>(s, kb, call, xn, xp, temp, L);
+    case 2: return dispatch_key<uint16_t>(s, kb, call, xn, xp, temp, L);
+    case 4: return dispatch_key<uint32_t>(s, kb, call, xn, xp, temp, L);
+    case 8: return dispatch_key<uint64_t>(s, kb, call, xn, xp, temp, L);
+    case 16: return dispatch_key<uint4>(s, kb, call, xn, xp, temp, L);
     }
     return B200ALG_UNSUPPORTED;
 }
@@ -1115,13 +1214,23 @@ extern "C" int b200alg_radix_sort_temp_bytes(int key_dtype, int64_t n, int value
 
 extern "C" int b200alg_radix_sort_keys(void *stream, void *keys, int64_t n, int64_t stride, int key_dtype, int order,
                                        void *temp, int64_t temp_bytes) {
-    return sort_common(stream, keys, stride, nullptr, n, key_dtype, 0, order, temp, temp_bytes);
+    const SortCall call{keys, keys, nullptr, nullptr, stride, n, nullptr, kSeqNone, false};
+    return sort_common(stream, call, key_dtype, 0, order, temp, temp_bytes);
 }
 
 extern "C" int b200alg_radix_sort_pairs(void *stream, void *keys, void *values, int64_t n, int key_dtype, int value_bytes,
                                         int order, void *temp, int64_t temp_bytes) {
     if (value_bytes == 0) return B200ALG_INVALID_ARGUMENT;
-    return sort_common(stream, keys, 1, values, n, key_dtype, value_bytes, order, temp, temp_bytes);
+    const SortCall call{keys, keys, values, values, 1, n, nullptr, kSeqNone, false};
+    return sort_common(stream, call, key_dtype, value_bytes, order, temp, temp_bytes);
+}
+
+extern "C" int b200alg_radix_sort_out_of_place(void *stream, const void *in_keys, const void *in_values, void *out_keys,
+                                               void *out_values, int64_t n, const int64_t *n_device, int key_dtype,
+                                               int value_bytes, int order, void *temp, int64_t temp_bytes) {
+    if (in_keys == out_keys || (value_bytes && in_values == out_values)) return B200ALG_INVALID_ARGUMENT;
+    const SortCall call{in_keys, out_keys, in_values, out_values, 1, n, (const long long *)n_device, kSeqNone, true};
+    return sort_common(stream, call, key_dtype, value_bytes, order, temp, temp_bytes);
 }
 
 extern "C" int b200alg_radix_sort_pairs_sequence(void *stream, void *keys, void *values, int64_t n, int key_dtype,
@@ -1129,7 +1238,8 @@ extern "C" int b200alg_radix_sort_pairs_sequence(void *stream, void *keys, void 
     const int vb = dtype_bytes(value_dtype);
     if (vb == 0) return B200ALG_UNSUPPORTED;
     const bool floating = value_dtype == B200ALG_F16 || value_dtype == B200ALG_F32 || value_dtype == B200ALG_F64;
-    return sort_common(stream, keys, 1, values, n, key_dtype, vb, order, temp, temp_bytes, floating ? kSeqFloating : kSeqInteger);
+    const SortCall call{keys, keys, values, values, 1, n, nullptr, floating ? kSeqFloating : kSeqInteger, false};
+    return sort_common(stream, call, key_dtype, vb, order, temp, temp_bytes);
 }
 
 extern "C" int b200alg_bucket_partition_temp_bytes(int key_dtype, int64_t n, int64_t *out_bytes) {

@@ -1,8 +1,11 @@
 """Radix sort, scan, reduce and histogram over the GPUs of one box.
 
-One process per GPU.  Each primitive shards the data, does its local work through the
-native library, and uses ``torch.distributed`` only for the exchange step the primitive
-really has:
+One process per GPU.  On GPUs the whole of it runs inside the native multi-GPU library
+(``include/b200alg_mg.h``: local kernels, NCCL for the few words each primitive exchanges,
+peer stores for the buckets of the sort); ``torch.distributed`` only carries the rendezvous
+token.  The same algorithms are also written out here over ``torch.distributed`` with a
+pluggable local engine; that path serves engines without the native library (the CPU
+engine of the tests over ``gloo``):
 
 * reduce, histogram - local kernel, then an all-reduce of one element / of the bins;
 * scan - local reduce, all-gather of the per-rank totals, fold of the lower ranks' totals,
@@ -24,11 +27,15 @@ import torch
 import torch.distributed as dist
 
 from . import _native as N
-from .algorithms import (Accelerator, B200AlgException, NotSupportedException, RadixSortOperation, ScanKind,
+from .algorithms import (Accelerator, ArgumentOutOfRangeException, B200AlgException, NotSupportedException, RadixSortOperation, ScanKind,
                          ScanReduceOperation, _ptr, _stream_ptr, dtype_code)
 
 _SIGNED_VIEW = {1: torch.int8, 2: torch.int16, 4: torch.int32, 8: torch.int64}
 _UNSIGNED = (torch.uint8, torch.uint16, torch.uint32, torch.uint64)
+
+
+def _stride_of(t: torch.Tensor) -> int:
+    return int(t.stride(0)) if t.dim() == 1 and t.numel() > 1 else 1
 
 
 def _signed_view(t: torch.Tensor) -> torch.Tensor:
@@ -201,17 +208,82 @@ def _fold_lower_ranks(totals: torch.Tensor, rank: int, op: ScanReduceOperation) 
     return pick(lower).reshape(1)
 
 
+class NativeComm:
+    """A communicator of the native multi-GPU library for this rank of a process group
+    (b200alg_comm_create_rank).  The process group only hands the rendezvous token round."""
+
+    def __init__(self, accelerator: Accelerator, group, sort_capacity: int):
+        self.acc = accelerator
+        self.M = N.mg_lib()
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.sort_capacity = int(sort_capacity)
+        token = [None]
+        if self.rank == 0:
+            buf = ctypes.create_string_buffer(N.UNIQUE_ID_BYTES)
+            B200AlgException.ThrowIfFailed(self.M.b200alg_comm_unique_id(buf))
+            token[0] = buf.raw
+        dist.broadcast_object_list(token, src=dist.get_global_rank(group, 0), group=group)
+        handle = ctypes.c_void_p()
+        with self.acc.Bind():
+            self._check(self.M.b200alg_comm_create_rank(token[0], self.world, self.rank, self.sort_capacity, ctypes.byref(handle)))
+        self.handle = handle
+
+    def _check(self, status: int) -> None:
+        if status == N.NCCL_ERROR:
+            raise B200AlgException(status)
+        B200AlgException.ThrowIfFailed(status)
+
+    def status(self, stream=None) -> None:
+        """Synchronises; raises when a bounded wait between GPUs ran out or a receive buffer was too small."""
+        with self.acc.Bind():
+            self._check(self.M.b200alg_comm_status(self.handle, _stream_ptr(stream)))
+
+    def destroy(self) -> None:
+        if self.handle is not None:
+            self.M.b200alg_comm_destroy(self.handle)
+            self.handle = None
+
+
 class ShardedAlgorithms:
     """The primitives over all ranks of a process group (one rank per GPU)."""
 
     SAMPLES_PER_RANK = 2048
     use_peer_scatter = True   # False: exchange the buckets with an NCCL all-to-all instead
+    use_native = True         # False: the torch.distributed formulation also on GPUs
 
-    def __init__(self, engine, group=None):
+    def __init__(self, engine, group=None, sort_capacity: int | None = None):
         self.engine = NativeEngine(engine) if isinstance(engine, Accelerator) else engine
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
+        self._sort_capacity = sort_capacity
+        self._comm: NativeComm | None = None
+
+    # -- native path --
+    def _native(self) -> bool:
+        return self.use_native and isinstance(self.engine, NativeEngine) and dist.get_backend(self.group) == "nccl"
+
+    def _communicator(self, sort_elements: int | None = None) -> NativeComm:
+        """The native communicator; (re)built collectively when the sort first needs a receive
+        buffer (its capacity: 1.3 x the largest shard, unless given at construction)."""
+        need_sort = sort_elements is not None and (self._comm is None or self._comm.sort_capacity == 0)
+        if self._comm is None or need_sort:
+            capacity = 0
+            if sort_elements is not None:
+                capacity = self._sort_capacity
+                if capacity is None:
+                    t = torch.tensor([sort_elements], dtype=torch.int64, device=self.engine.device)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+                    capacity = int(int(t.item()) * 1.3) + (1 << 16)
+            if self._comm is not None:
+                self._comm.destroy()
+            self._comm = NativeComm(self.engine.acc, self.group, capacity)
+        return self._comm
+
+    def CheckStatus(self) -> None:
+        if self._comm is not None:
+            self._comm.status()
 
     # -- collectives on bit patterns --
     def _all_gather(self, t: torch.Tensor) -> torch.Tensor:
@@ -237,6 +309,13 @@ class ShardedAlgorithms:
     # -- reduce --
     def Reduce(self, view: torch.Tensor, operation: ScanReduceOperation) -> torch.Tensor:
         """Every rank gets the fold over all shards (one element)."""
+        if self._native():
+            c = self._communicator()
+            out = self.engine.empty(1, operation.dtype)
+            with self.engine.acc.Bind():
+                c._check(c.M.b200alg_reduce_mg(c.handle, _stream_ptr(None), _ptr(view), _stride_of(view), view.numel(),
+                                               dtype_code(operation.dtype), operation.op, _ptr(out)))
+            return out
         out = self.engine.reduce(view, operation)
         self._all_reduce(out, operation.op)
         return out
@@ -245,6 +324,14 @@ class ShardedAlgorithms:
     def Histogram(self, view, histogram, histogramOverflow, locator) -> None:
         """Adds the counts of all shards to every rank's ``histogram`` (replicas must agree
         on entry); ``histogramOverflow`` may be None (unchecked)."""
+        if self._native():
+            c = self._communicator()
+            with self.engine.acc.Bind():
+                c._check(c.M.b200alg_histogram_mg(c.handle, _stream_ptr(None), _ptr(view), _stride_of(view), view.numel(),
+                                                  dtype_code(view.dtype), locator.code, float(locator.lo), float(locator.hi),
+                                                  _ptr(histogram), histogram.numel(), dtype_code(histogram.dtype),
+                                                  _ptr(histogramOverflow)))
+            return
         local = torch.zeros_like(histogram)
         self.engine.histogram(view, local, None, locator)
         self._all_reduce(local, N.ADD)
@@ -268,6 +355,16 @@ class ShardedAlgorithms:
     # -- scan --
     def Scan(self, input: torch.Tensor, output: torch.Tensor, operation: ScanReduceOperation, kind: ScanKind) -> None:
         """Scan of the concatenation of all ranks' inputs (rank order); each rank writes its slice."""
+        if self._native() and _stride_of(input) == 1 and _stride_of(output) == 1:
+            c = self._communicator()
+            n = input.numel()
+            acc = self.engine.acc
+            temp = self.engine._temp("scan", acc.ComputeScanTempStorageSize(operation.dtype, max(n, 1)))
+            with acc.Bind():
+                c._check(c.M.b200alg_scan_mg(c.handle, _stream_ptr(None), _ptr(input), _ptr(output), n,
+                                             dtype_code(operation.dtype), operation.op, int(kind == ScanKind.Inclusive),
+                                             _ptr(temp), temp.numel() * 4))
+            return
         if input.numel() == 0:
             total = _identity_tensor(operation, input.device)
         else:
@@ -372,10 +469,39 @@ class ShardedAlgorithms:
             eng.sort(recv_keys, recv_values, operation)
         return recv_keys, recv_values
 
+    def SortAsync(self, keys: torch.Tensor, values: torch.Tensor | None, operation: RadixSortOperation):
+        """Enqueues the whole sort without a host synchronisation (native path only) and returns
+        ``(out_keys, out_values, count)``: buffers of the communicator's capacity whose first
+        ``count[0]`` elements (an int64 on the device) are rank r's slice of the sorted whole."""
+        if keys.dtype != operation.dtype:
+            raise NotSupportedException(f"keys are {keys.dtype}, operation sorts {operation.dtype}")
+        if values is not None and values.dtype.itemsize not in (4, 8):
+            raise NotSupportedException("values of 4 or 8 bytes")
+        if not self._native():
+            raise NotSupportedException("the asynchronous sort needs the native multi-GPU library")
+        c = self._communicator(sort_elements=keys.numel())
+        if keys.numel() > c.sort_capacity:
+            raise ArgumentOutOfRangeException("the shard is larger than the communicator's sort capacity")
+        cap = c.sort_capacity
+        out_keys = self.engine.empty(cap, keys.dtype)
+        out_values = None if values is None else self.engine.empty(cap, values.dtype)
+        count = self.engine.empty(1, torch.int64)
+        with self.engine.acc.Bind():
+            c._check(c.M.b200alg_sort_mg(c.handle, _stream_ptr(None), _ptr(keys), _ptr(values), keys.numel(),
+                                         dtype_code(keys.dtype), 0 if values is None else values.dtype.itemsize,
+                                         N.SORT_DESCENDING if operation.descending else 0, _ptr(out_keys), _ptr(out_values),
+                                         cap, _ptr(count)))
+        return out_keys, out_values, count
+
     def SortKeys(self, keys: torch.Tensor, operation: RadixSortOperation):
         """Returns ``(sorted_slice, count)``: rank r holds the r-th slice of the sorted whole."""
         if keys.dtype != operation.dtype:
             raise NotSupportedException(f"keys are {keys.dtype}, operation sorts {operation.dtype}")
+        if self._native():
+            out, _, count = self.SortAsync(keys, None, operation)
+            self.CheckStatus()                      # synchronises: the slice length is needed on the host now
+            m = int(count.item())
+            return out[:m], m
         out, _ = self._sort(keys, None, operation)
         return out, out.numel()
 
@@ -385,6 +511,11 @@ class ShardedAlgorithms:
             raise NotSupportedException(f"keys are {keys.dtype}, operation sorts {operation.dtype}")
         if values.dtype.itemsize not in (4, 8):
             raise NotSupportedException("values of 4 or 8 bytes")
+        if self._native():
+            out, outv, count = self.SortAsync(keys, values, operation)
+            self.CheckStatus()
+            m = int(count.item())
+            return out[:m], outv[:m]
         return self._sort(keys, values, operation)
 
     def sort_launches_per_step(self, operation: RadixSortOperation) -> int:
@@ -392,4 +523,8 @@ class ShardedAlgorithms:
         sort (histogram, offsets, one pass per key byte, copy-back each) and the partition
         (bucket histogram, offsets, count export, one pass)."""
         passes = operation.dtype.itemsize
+        if self._native():
+            # samples, collect, splitters, plan, capacity word, 2 barriers; two sorts (histogram,
+            # offsets, passes, copy-back); bucket sizes (3) and the partition (2)
+            return 7 + 2 * (3 + passes) + 5
         return 2 * (3 + passes) + 4

@@ -64,7 +64,8 @@ typedef enum {
     B200ALG_WAIT_LIMIT = 5,         /* a device-side wait ran out (reported by b200alg_device_status) */
     B200ALG_MISALIGNED = 6,         /* a pointer is not aligned to its element size / temp not to 256 */
     B200ALG_TOO_LARGE = 7,          /* n beyond 2^38; the int.MaxValue limit of the reference (ErrorMessages.NotSupportedArrayView64) is the host mirror's check */
-    B200ALG_STATIC_LIMIT = 8        /* n beyond what an entry point with built-in scratch accepts */
+    B200ALG_STATIC_LIMIT = 8,       /* n beyond what an entry point with built-in scratch accepts */
+    B200ALG_NCCL_ERROR = 9          /* multi-GPU layer (b200alg_mg.h): a NCCL call failed */
 } b200alg_status;
 
 int b200alg_version(void);
@@ -101,6 +102,17 @@ int b200alg_radix_sort_pairs(void *stream, void *keys, void *values, int64_t n, 
  * b200alg_radix_sort_temp_bytes with value_bytes = the size of value_dtype. */
 int b200alg_radix_sort_pairs_sequence(void *stream, void *keys, void *values, int64_t n, int key_dtype,
                                       int value_dtype, int order, void *temp, int64_t temp_bytes);
+
+/* The same sort out of place: in_keys / in_values are only read, the result lands in
+ * out_keys / out_values (dense views, distinct from the inputs).  No counterpart in the
+ * reference (its sorts are in place); the last step of a sort that spans several GPUs uses
+ * it to sort straight out of its receive buffer.  n_device, when not NULL, points to the
+ * element count in device memory (int64): n is then only an upper bound that sizes temp and
+ * the launches, and nothing beyond *n_device elements is read or written - the count may
+ * still be produced by earlier work on the same stream when this call is enqueued. */
+int b200alg_radix_sort_out_of_place(void *stream, const void *in_keys, const void *in_values, void *out_keys,
+                                    void *out_values, int64_t n, const int64_t *n_device, int key_dtype,
+                                    int value_bytes, int order, void *temp, int64_t temp_bytes);
 
 /* Stable partition of a shard into num_splitters + 1 buckets: the first step of a sort
  * that spans several GPUs (new surface; the reference has no multi-device sort, its only

@@ -27,6 +27,19 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), name
 
 
+def test_multi_gpu_library_exports_what_its_header_declares():
+    text = open(os.path.join(ROOT, "include", "b200alg_mg.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    declared = sorted(set(re.findall(r"\b(b200alg_[a-z0-9_]+)\s*\(", text)))
+    assert sorted(_native.MG_SIGNATURES) == declared
+    lib = _native.mg_lib()
+    for name in declared:
+        assert hasattr(lib, name), name
+    # argument errors come back before any CUDA or NCCL call
+    assert lib.b200alg_comm_unique_id(None) == _native.INVALID_ARGUMENT
+    assert lib.b200alg_comm_status(None, None) == _native.INVALID_ARGUMENT
+
+
 def test_host_only_entry_points():
     L = _native.lib()
     assert L.b200alg_version() == 100

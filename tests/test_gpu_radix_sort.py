@@ -211,3 +211,43 @@ def test_pairs_with_sequencer_when_every_key_is_equal(accelerator):
     accelerator.CreateRadixSortPairs(op, sequencer=ib.Sequencers)(None, dk, dv, ib.Sequencers.IndexSequencer, temp)
     np.testing.assert_array_equal(to_host(dv), np.arange(n, dtype=np.int32))
     np.testing.assert_array_equal(to_host(dk), np.full(n, 7, dtype=np.uint32))
+
+
+@pytest.mark.parametrize("key_t,val_t", [("UInt32", None), ("UInt64", "UInt32"), ("Int16", "Int64"), ("UInt8", None)])
+@pytest.mark.parametrize("n,count", [(1, 1), (4097, 4097), (250_003, 250_003), (250_003, 99_999), (250_003, 0), (8192, 8191)])
+def test_out_of_place_sort_with_a_device_side_count(accelerator, key_t, val_t, n, count):
+    """b200alg_radix_sort_out_of_place: the input stays untouched, only the first *n_device
+    elements are sorted into the output, and nothing beyond them is written."""
+    import ctypes
+    from ilgpu_b200 import _native as N
+    from ilgpu_b200.algorithms import dtype_code
+    L = N.lib()
+    rng = np.random.default_rng(n + count)
+    span = 50 if val_t else 2 ** 16
+    keys = rng.integers(0, min(span, np.iinfo(NP[key_t]).max), size=n).astype(NP[key_t])
+    if key_t == "Int16":
+        keys = (keys - 25).astype(NP[key_t])
+    values = None if val_t is None else rng.integers(0, 2 ** 31, size=n).astype(NP[val_t])
+    dk = to_device(keys)
+    dv = None if values is None else to_device(values)
+    sentinel_k = np.full(n, 0x5A, dtype=np.uint8).repeat(keys.itemsize).view(NP[key_t])[:n]
+    ok = to_device(sentinel_k.copy())
+    ov = None if values is None else to_device(np.full(n, 77).astype(NP[val_t]))
+    dn = torch.tensor([count], dtype=torch.int64, device="cuda")
+    vb = 0 if values is None else values.itemsize
+    need = ctypes.c_int64(0)
+    assert L.b200alg_radix_sort_temp_bytes(dtype_code(dk.dtype), n, vb, ctypes.byref(need)) == N.OK
+    temp = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+    p = lambda t: ctypes.c_void_p(0 if t is None else t.data_ptr())
+    rc = L.b200alg_radix_sort_out_of_place(None, p(dk), p(dv), p(ok), p(ov), n, p(dn), dtype_code(dk.dtype), vb, 0,
+                                           p(temp), need.value)
+    assert rc == N.OK
+    assert L.b200alg_device_status(None, p(temp)) == N.OK
+    ek, ev = oracle.radix_sort(keys[:count], None if values is None else values[:count])
+    np.testing.assert_array_equal(to_host(dk), keys)                       # input untouched
+    np.testing.assert_array_equal(to_host(ok)[:count], ek)
+    np.testing.assert_array_equal(to_host(ok)[count:], sentinel_k[count:])  # nothing written past the count
+    if values is not None:
+        np.testing.assert_array_equal(to_host(dv), values)
+        np.testing.assert_array_equal(to_host(ov)[:count], ev)
+        np.testing.assert_array_equal(to_host(ov)[count:], np.full(n - count, 77).astype(NP[val_t]))
