@@ -812,6 +812,11 @@ static int configure_persistent(KernelT kernel, int threads, size_t bytes, int *
     return B200ALG_OK;
 }
 
+// Measurement hook (b200alg_testing_time_sort_pass): events recorded around one digit pass of
+// the calling thread's next sort.
+thread_local cudaEvent_t g_timed_pass_events[2] = {nullptr, nullptr};
+thread_local int g_timed_pass = -1;
+
 // What a sort call works on, untyped (the entry points fill this in).
 struct SortCall {
     const void *in_keys;
@@ -885,8 +890,10 @@ static int run_passes(cudaStream_t s, const SortCall &call, const KeyXform<K> &x
         RadixDigit<K, XF> dg;
         if constexpr (std::is_same<XF, KeyXform<K>>::value) dg.xf = xf;
         dg.shift = p * 8;
+        if (g_timed_pass == p) B200ALG_CUDA_TRY(cudaEventRecord(g_timed_pass_events[0], s));
         kernel<<<grid, THREADS, Smem::bytes, s>>>(io, p, dg, hdr, gbase, status, (int)L.tiles, call.value_seq);
         B200ALG_LAUNCH_CHECK();
+        if (g_timed_pass == p) B200ALG_CUDA_TRY(cudaEventRecord(g_timed_pass_events[1], s));
     }
     {
         int64_t want = ceil_div(n, 256 * 8);
@@ -1240,6 +1247,27 @@ extern "C" int b200alg_radix_sort_pairs_sequence(void *stream, void *keys, void 
     const bool floating = value_dtype == B200ALG_F16 || value_dtype == B200ALG_F32 || value_dtype == B200ALG_F64;
     const SortCall call{keys, keys, values, values, 1, n, nullptr, floating ? kSeqFloating : kSeqInteger, false};
     return sort_common(stream, call, key_dtype, vb, order, temp, temp_bytes);
+}
+
+extern "C" int b200alg_testing_time_sort_pass(void *stream, void *keys, int64_t n, int key_dtype, int order, void *temp,
+                                              int64_t temp_bytes, int pass, float *milliseconds) {
+    if (!milliseconds || pass < 0 || pass >= kMaxPasses) return B200ALG_INVALID_ARGUMENT;
+    cudaEvent_t ev[2];
+    B200ALG_CUDA_TRY(cudaEventCreate(&ev[0]));
+    B200ALG_CUDA_TRY(cudaEventCreate(&ev[1]));
+    g_timed_pass_events[0] = ev[0];
+    g_timed_pass_events[1] = ev[1];
+    g_timed_pass = pass;
+    const int rc = b200alg_radix_sort_keys(stream, keys, n, 1, key_dtype, order, temp, temp_bytes);
+    g_timed_pass = -1;
+    int result = rc;
+    if (rc == B200ALG_OK) {
+        if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess || cudaEventElapsedTime(milliseconds, ev[0], ev[1]) != cudaSuccess)
+            result = B200ALG_CUDA_ERROR;
+    }
+    cudaEventDestroy(ev[0]);
+    cudaEventDestroy(ev[1]);
+    return result;
 }
 
 extern "C" int b200alg_bucket_partition_temp_bytes(int key_dtype, int64_t n, int64_t *out_bytes) {

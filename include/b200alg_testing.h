@@ -18,6 +18,14 @@ extern "C" {
  * B200ALG_WAIT_LIMIT.  temp: at least 512 bytes, 256-byte aligned. */
 int b200alg_testing_wait_limit(void *stream, void *temp, int64_t temp_bytes, unsigned int max_polls);
 
+/* b200alg_radix_sort_keys (dense view) with CUDA events around digit pass `pass` (0 = least
+ * significant byte) on `stream`; synchronises the stream and returns the pass's device time.
+ * The sort call is one entry point, so a caller cannot bracket a single pass by itself; the
+ * benchmark uses this for the roofline figure of the digit-pass kernel.  A pass whose digit is
+ * constant over all keys exits at once and reads as a few microseconds. */
+int b200alg_testing_time_sort_pass(void *stream, void *keys, int64_t n, int key_dtype, int order, void *temp,
+                                   int64_t temp_bytes, int pass, float *milliseconds);
+
 #ifdef __cplusplus
 }
 #endif
