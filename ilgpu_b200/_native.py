@@ -48,6 +48,8 @@ SIGNATURES = {
     "b200alg_sequence": (_int, [_vp, _vp, _i64, _int, _i64, _i64]),
     "b200alg_unique_temp_bytes": (_int, [_int, _i64, ctypes.POINTER(_i64)]),
     "b200alg_unique": (_int, [_vp, _vp, _i64, _int, _vp, _vp, _i64]),
+    "b200alg_run_length_encode_temp_bytes": (_int, [_int, _i64, ctypes.POINTER(_i64)]),
+    "b200alg_run_length_encode": (_int, [_vp, _vp, _i64, _int, _vp, _vp, _vp, _vp, _i64]),
     "b200alg_device_status": (_int, [_vp, _vp]),
 }
 

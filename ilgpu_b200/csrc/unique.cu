@@ -33,8 +33,8 @@ template <> struct SameValue<__half> {
 
 template <typename T>
 __global__ void __launch_bounds__(kUniqueThreads)
-unique_select_kernel(const T *__restrict__ in, int64_t n, T *__restrict__ kept, long long *out_count, TempHeader *hdr,
-                     void *state_base, int num_tiles) {
+unique_select_kernel(const T *__restrict__ in, int64_t n, T *__restrict__ kept, long long *__restrict__ starts,
+                     long long *out_count, TempHeader *hdr, void *state_base, int num_tiles) {
     __shared__ unsigned int warp_total[kUniqueThreads / 32];
     __shared__ unsigned int warp_excl[kUniqueThreads / 32];
     __shared__ unsigned int s_prefix;
@@ -125,8 +125,21 @@ unique_select_kernel(const T *__restrict__ in, int64_t n, T *__restrict__ kept, 
     unsigned int pos = s_prefix + warp_excl[warp] + (incl - count);
 #pragma unroll
     for (int k = 0; k < kUniqueItems; ++k) {
-        if ((keep_mask >> k) & 1u) kept[pos++] = item[k];
+        if ((keep_mask >> k) & 1u) {
+            kept[pos] = item[k];
+            if (starts) starts[pos] = first + k;  // where the run begins (run-length encoding)
+            ++pos;
+        }
     }
+}
+
+// lengths[r] = distance from the start of run r to the start of the next run (or to n).
+__global__ void __launch_bounds__(256)
+run_lengths_kernel(const long long *starts, const long long *count, long long n, long long *lengths) {
+    const long long m = *count;
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < m; r += step)
+        lengths[r] = (r + 1 < m ? starts[r + 1] : n) - starts[r];
 }
 
 template <typename T>
@@ -154,8 +167,9 @@ template <typename T>
 static int run_unique(cudaStream_t s, void *data, int64_t n, void *out_count, void *temp, const UniqueLayout &L) {
     char *t = (char *)temp;
     B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)L.off_kept, s));
-    unique_select_kernel<T><<<(int)L.tiles, kUniqueThreads, 0, s>>>((const T *)data, n, (T *)(t + L.off_kept), (long long *)out_count,
-                                                                  (TempHeader *)temp, t + L.off_state, (int)L.tiles);
+    unique_select_kernel<T><<<(int)L.tiles, kUniqueThreads, 0, s>>>((const T *)data, n, (T *)(t + L.off_kept), nullptr,
+                                                                  (long long *)out_count, (TempHeader *)temp, t + L.off_state,
+                                                                  (int)L.tiles);
     B200ALG_LAUNCH_CHECK();
     int64_t want = ceil_div(n, 256 * 8);
     const int64_t cap = (int64_t)sm_count() * 8;
@@ -165,9 +179,77 @@ static int run_unique(cudaStream_t s, void *data, int64_t n, void *out_count, vo
     return B200ALG_OK;
 }
 
+// Run-length encoding: the same selection, with the survivors written to the caller's array
+// and the run starts to scratch, from which the lengths follow.
+struct RunLengthLayout {
+    int64_t tiles, off_state, off_starts, total;
+};
+static RunLengthLayout run_length_layout(int64_t n) {
+    RunLengthLayout L;
+    L.tiles = ceil_div(n < 1 ? 1 : n, kUniqueTile);
+    L.off_state = sizeof(TempHeader);
+    L.off_starts = L.off_state + round_up(L.tiles * kDescStride, 256);
+    L.total = L.off_starts + round_up((n < 1 ? 1 : n) * 8, 256);
+    return L;
+}
+
+template <typename T>
+static int run_rle(cudaStream_t s, const void *data, int64_t n, void *values, void *lengths, void *num_runs, void *temp,
+                   const RunLengthLayout &L) {
+    char *t = (char *)temp;
+    B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)L.off_starts, s));
+    unique_select_kernel<T><<<(int)L.tiles, kUniqueThreads, 0, s>>>((const T *)data, n, (T *)values, (long long *)(t + L.off_starts),
+                                                                  (long long *)num_runs, (TempHeader *)temp, t + L.off_state,
+                                                                  (int)L.tiles);
+    B200ALG_LAUNCH_CHECK();
+    int64_t want = ceil_div(n, 256 * 8);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    const int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    run_lengths_kernel<<<blocks, 256, 0, s>>>((const long long *)(t + L.off_starts), (const long long *)num_runs, (long long)n,
+                                              (long long *)lengths);
+    B200ALG_LAUNCH_CHECK();
+    return B200ALG_OK;
+}
+
 }  // namespace b200alg
 
 using namespace b200alg;
+
+extern "C" int b200alg_run_length_encode_temp_bytes(int dtype, int64_t n, int64_t *out_bytes) {
+    if (!out_bytes || n < 0) return B200ALG_INVALID_ARGUMENT;
+    if (dtype_bytes(dtype) == 0) return B200ALG_UNSUPPORTED;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
+    *out_bytes = run_length_layout(n).total;
+    return B200ALG_OK;
+}
+
+extern "C" int b200alg_run_length_encode(void *stream, const void *data, int64_t n, int dtype, void *values, int64_t *lengths,
+                                         int64_t *num_runs, void *temp, int64_t temp_bytes) {
+    if (!num_runs || n < 0) return B200ALG_INVALID_ARGUMENT;
+    if ((uintptr_t)num_runs % 8) return B200ALG_MISALIGNED;
+    if (n == 0) {
+        B200ALG_CUDA_TRY(cudaMemsetAsync(num_runs, 0, 8, (cudaStream_t)stream));
+        return B200ALG_OK;
+    }
+    if (!data || !values || !lengths || !temp) return B200ALG_INVALID_ARGUMENT;
+    const int es = dtype_bytes(dtype);
+    if (es == 0) return B200ALG_UNSUPPORTED;
+    if (n > kMaxElements) return B200ALG_TOO_LARGE;
+    if (((uintptr_t)data % es) || ((uintptr_t)values % es) || ((uintptr_t)lengths % 8) || ((uintptr_t)temp % 256)) return B200ALG_MISALIGNED;
+    const RunLengthLayout L = run_length_layout(n);
+    if (temp_bytes < L.total) return B200ALG_TEMP_TOO_SMALL;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (dtype) {
+    case B200ALG_I8: case B200ALG_U8: return run_rle<uint8_t>(s, data, n, values, lengths, num_runs, temp, L);
+    case B200ALG_I16: case B200ALG_U16: return run_rle<uint16_t>(s, data, n, values, lengths, num_runs, temp, L);
+    case B200ALG_I32: case B200ALG_U32: return run_rle<uint32_t>(s, data, n, values, lengths, num_runs, temp, L);
+    case B200ALG_I64: case B200ALG_U64: return run_rle<uint64_t>(s, data, n, values, lengths, num_runs, temp, L);
+    case B200ALG_F16: return run_rle<__half>(s, data, n, values, lengths, num_runs, temp, L);
+    case B200ALG_F32: return run_rle<float>(s, data, n, values, lengths, num_runs, temp, L);
+    case B200ALG_F64: return run_rle<double>(s, data, n, values, lengths, num_runs, temp, L);
+    }
+    return B200ALG_UNSUPPORTED;
+}
 
 extern "C" int b200alg_unique_temp_bytes(int dtype, int64_t n, int64_t *out_bytes) {
     if (!out_bytes || n < 0) return B200ALG_INVALID_ARGUMENT;

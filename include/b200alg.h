@@ -205,6 +205,16 @@ int b200alg_sequence(void *stream, void *view, int64_t n, int dtype, int64_t sta
 int b200alg_unique_temp_bytes(int dtype, int64_t n, int64_t *out_bytes);
 int b200alg_unique(void *stream, void *data, int64_t n, int dtype, void *out_count, void *temp, int64_t temp_bytes);
 
+/* Run-length encoding: the step after a sort when the counts per key are wanted (sort ->
+ * unique -> counts).  values[r] = the element that starts run r of data[0..n), lengths[r]
+ * (int64) = how many consecutive equal elements it has, num_runs[0] (int64, device) = the
+ * number of runs; `data` is only read; values and lengths need room for n entries in the
+ * worst case.  Equality as in b200alg_unique.  No counterpart in the reference (its
+ * UniqueExtensions drop the duplicates without counting them). */
+int b200alg_run_length_encode_temp_bytes(int dtype, int64_t n, int64_t *out_bytes);
+int b200alg_run_length_encode(void *stream, const void *data, int64_t n, int dtype, void *values, int64_t *lengths,
+                              int64_t *num_runs, void *temp, int64_t temp_bytes);
+
 /* Device-side waits (decoupled look-back) are bounded; when one runs out the kernel
  * records it in `temp` and finishes.  This call copies that record back and
  * SYNCHRONISES `stream`: returns B200ALG_OK or B200ALG_WAIT_LIMIT. */

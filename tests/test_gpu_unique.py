@@ -73,3 +73,35 @@ def test_empty_and_count_only_output(accelerator):
     temp = accelerator.Allocate1D(256, torch.int32)
     accelerator.CreateUnique(torch.int32)(None, data, out, temp)
     assert int(out.cpu()[0]) == 0
+
+
+@pytest.mark.parametrize("tname", ["UInt8", "Int32", "UInt64", "Float", "Half"])
+@pytest.mark.parametrize("n", [1, 2, 4095, 4096, 4097, 1_000_003])
+def test_run_length_encode(tname, n):
+    """values / lengths / number of runs against numpy's run boundaries (equality as in Unique:
+    NaNs are equal to each other)."""
+    import ctypes
+    from ilgpu_b200 import _native as N
+    from ilgpu_b200.algorithms import dtype_code
+    L = N.lib()
+    rng = np.random.default_rng(n)
+    host = np.repeat(rng.integers(0, 5, size=n), rng.integers(1, 9, size=n))[:n].astype(NP[tname])
+    if tname in ("Float", "Half") and n > 10:
+        host[3:6] = np.nan
+    dev = to_device(host)
+    values = torch.zeros_like(dev)
+    lengths = torch.zeros(n, dtype=torch.int64, device="cuda")
+    runs = torch.zeros(1, dtype=torch.int64, device="cuda")
+    need = ctypes.c_int64(0)
+    assert L.b200alg_run_length_encode_temp_bytes(dtype_code(dev.dtype), n, ctypes.byref(need)) == N.OK
+    temp = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    assert L.b200alg_run_length_encode(None, p(dev), n, dtype_code(dev.dtype), p(values), p(lengths), p(runs), p(temp), need.value) == N.OK
+    assert L.b200alg_device_status(None, p(temp)) == N.OK
+    same = (host[1:] == host[:-1]) | ((host[1:] != host[1:]) & (host[:-1] != host[:-1]))
+    starts = np.concatenate([[0], np.nonzero(~same)[0] + 1])
+    m = int(runs.cpu()[0])
+    assert m == len(starts)
+    np.testing.assert_array_equal(to_host(lengths)[:m], np.diff(np.concatenate([starts, [n]])))
+    np.testing.assert_array_equal(to_host(values)[:m].view(np.uint8), host[starts].view(np.uint8))
+    np.testing.assert_array_equal(to_host(dev).view(np.uint8), host.view(np.uint8))     # the input is only read
