@@ -12,10 +12,7 @@ enum : unsigned int { kInvalid = 0u, kAggregate = 1u, kInclusive = 2u };
 // {flag, value} into one 64-bit word that is read and written with single (relaxed)
 // accesses.  8-byte types keep the two partial results in separate slots of the record and
 // publish the flag with release / acquire.
-#ifndef B200ALG_SCAN_DESC_STRIDE
-#define B200ALG_SCAN_DESC_STRIDE 128
-#endif
-constexpr int kDescStride = B200ALG_SCAN_DESC_STRIDE;
+constexpr int kDescStride = 128;
 static_assert(kDescStride >= 32 && kDescStride % 32 == 0, "a record holds flag + two 8-byte values");
 
 template <typename T, int BYTES = sizeof(T)> struct TileState;

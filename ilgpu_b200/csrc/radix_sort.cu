@@ -322,7 +322,10 @@ template <> struct IndexOf<unsigned long long> { using type = unsigned long long
 // Full dense tiles are staged in shared memory by one bulk asynchronous copy (TMA, no
 // multicast) that is issued a tile ahead.
 constexpr bool kSortTma = true;
-constexpr int kLookWindow = 4;  // predecessors examined per look-back round
+constexpr int kLookWindow = 4;  // predecessors examined per look-back round (2 and 8 measured slower)
+// The digit passes are launched as programmatic dependents of one another: the blocks of the
+// next pass move in as those of this one leave and do their set-up before they wait for it.
+constexpr bool kSortPdl = true;
 
 template <typename K, typename V, bool KEEP_DIGITS, int THREADS, int ITEMS>
 struct OnesweepSmem {
@@ -671,8 +674,16 @@ onesweep_kernel(SortBuffers<K, V> io, int pass, Digit dg, TempHeader *hdr, const
     static_assert(THREADS >= 2 * kRadix, "one thread per digit for the offsets and one for the look-back");
     using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
 
-    if (hdr->reserved[kCtlSkip + pass]) return;
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    if (kSortPdl) {
+        grid_dependency_release();  // the next kernel of the call may take the SMs this one leaves
+        {   // meanwhile: the part of the set-up that reads nothing
+            uint4 *zm = reinterpret_cast<uint4 *>(smem_raw + L::off_mask);
+            for (int i = threadIdx.x; i < (THREADS / 32) * kRadix / 4; i += THREADS) zm[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        grid_dependency_wait();     // everything the kernels before this one wrote is visible from here on
+    }
+    if (hdr->reserved[kCtlSkip + pass]) return;
     // The pass description lives in shared memory: a dozen pointers that would otherwise sit
     // in registers for the whole kernel.
     static_assert(sizeof(PassContext<K, V, SW>) <= 128, "context slot");
@@ -766,21 +777,19 @@ struct SortLayout {
     int64_t off_ghist, off_gbase, off_status, control_bytes, off_keys, off_values, total;
 };
 
-#ifndef B200ALG_SORT_THREADS
-#define B200ALG_SORT_THREADS 512
-#endif
-#ifndef B200ALG_SORT_ITEMS
-#define B200ALG_SORT_ITEMS 16
-#endif
+// Block shape of the digit pass: 512 threads, two blocks per SM, 8192 keys per tile (4096 for
+// 8-byte keys).  256- and 1024-thread blocks, 12 and 24 items per thread all measured slower.
+constexpr int kSortThreads = 512;
+constexpr int kSortItems = 16;
 template <typename K> struct SortTuning {
-    static constexpr int THREADS = B200ALG_SORT_THREADS;
-    static constexpr int ITEMS = sizeof(K) == 8 ? B200ALG_SORT_ITEMS / 2 : B200ALG_SORT_ITEMS;
+    static constexpr int THREADS = kSortThreads;
+    static constexpr int ITEMS = sizeof(K) == 8 ? kSortItems / 2 : kSortItems;
 };
 
 static SortLayout sort_layout(int key_bytes, int value_bytes, int64_t n) {
     SortLayout L;
     L.passes = key_bytes;
-    L.tile = B200ALG_SORT_THREADS * (key_bytes == 8 ? B200ALG_SORT_ITEMS / 2 : B200ALG_SORT_ITEMS);
+    L.tile = kSortThreads * (key_bytes == 8 ? kSortItems / 2 : kSortItems);
     L.tiles = ceil_div(n < 1 ? 1 : n, L.tile);
     L.wide_status = n >= (1ll << 30);
     L.off_ghist = sizeof(TempHeader);
@@ -891,8 +900,13 @@ static int run_passes(cudaStream_t s, const SortCall &call, const KeyXform<K> &x
         if constexpr (std::is_same<XF, KeyXform<K>>::value) dg.xf = xf;
         dg.shift = p * 8;
         if (g_timed_pass == p) B200ALG_CUDA_TRY(cudaEventRecord(g_timed_pass_events[0], s));
-        kernel<<<grid, THREADS, Smem::bytes, s>>>(io, p, dg, hdr, gbase, status, (int)L.tiles, call.value_seq);
-        B200ALG_LAUNCH_CHECK();
+        if (kSortPdl) {
+            B200ALG_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(THREADS), Smem::bytes, s, io, p, dg, hdr,
+                                              (const unsigned long long *)gbase, status, (int)L.tiles, call.value_seq));
+        } else {
+            kernel<<<grid, THREADS, Smem::bytes, s>>>(io, p, dg, hdr, gbase, status, (int)L.tiles, call.value_seq);
+            B200ALG_LAUNCH_CHECK();
+        }
         if (g_timed_pass == p) B200ALG_CUDA_TRY(cudaEventRecord(g_timed_pass_events[1], s));
     }
     {
