@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "rank_barrier.cuh"
 #include "../../include/b200alg_mg.h"
 
 namespace b200alg {
@@ -107,22 +108,21 @@ __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int *p
 
 // Barrier over the ranks, on the stream: thread b tells rank b that this rank has reached
 // generation `epoch` (a store into rank b's flag array, which is mapped here) and waits until
-// rank b has said the same here.  The wait is bounded; when it runs out the kernel records
-// that and returns.  Generations compare modulo 2^32.
+// rank b has said the same here (rank_barrier.cuh).  The wait is bounded; when it runs out the
+// kernel records that and returns.
+struct SystemScopeMemory {
+    __device__ void store_release(unsigned int *p, unsigned int v) { st_release_sys_u32(p, v); }
+    __device__ unsigned int load_acquire(const unsigned int *p) { return ld_acquire_sys_u32(p); }
+    __device__ void pause() { __nanosleep(200); }
+};
 __global__ void rank_barrier_kernel(unsigned int *const *peer_flags, const unsigned int *my_flags, int rank, int ranks,
                                     unsigned int epoch, TempHeader *hdr) {
     const int b = threadIdx.x;
     if (b >= ranks) return;
+    SystemScopeMemory mem;
     __threadfence_system();  // everything this GPU wrote before (peer stores of the kernel before) goes first
-    st_release_sys_u32(peer_flags[b] + rank, epoch);
-    unsigned int polls = 0;
-    while ((int)(ld_acquire_sys_u32(my_flags + b) - epoch) < 0) {
-        if (++polls > kMaxFlagPolls) {
-            atomicExch(&hdr->wait_limit_hit, 1u);
-            break;
-        }
-        __nanosleep(200);
-    }
+    rank_barrier_signal(mem, peer_flags[b], rank, epoch);
+    if (!rank_barrier_wait(mem, my_flags, b, epoch, kMaxFlagPolls)) atomicExch(&hdr->wait_limit_hit, 1u);
 }
 
 // ---- reduce / scan helpers -----------------------------------------------------------------
