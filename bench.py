@@ -229,7 +229,9 @@ def secondary_metrics(acc, peak_gbs: float) -> dict:
         red(None, x, cell)
     out["reduce_f32_sum_2^30"] = gbs(4 * n, time_region(lambda i: red(None, x, cell), 5, stream))
     del x, y, temp
-    # int32 reduce + exclusive scan over 2^24 values, rotating over 8 buffers (64 MiB each)
+    # int32 reduce + exclusive scan over 2^24 values, rotating over 8 buffers (64 MiB each).  A call
+    # is 20 to 40 us of device work, less than what the Python layer needs to enqueue it, so the
+    # 16 calls are also captured into a CUDA graph and replayed: that figure is the device's.
     n = 1 << 24
     bufs = [synthetic.uniform_int32_device(n, 1, "cuda", start=i * n) for i in range(8)]
     outs = [torch.empty_like(b) for b in bufs]
@@ -239,8 +241,39 @@ def secondary_metrics(acc, peak_gbs: float) -> dict:
     cell = acc.Allocate1D(1, torch.int32)
     for i in range(8):
         scan(None, bufs[i], outs[i], temp); red(None, bufs[i], cell)
-    out["scan_i32_exclusive_2^24"] = gbs(8 * n, time_region(lambda i: scan(None, bufs[i % 8], outs[i % 8], temp), 16, stream))
-    out["reduce_i32_sum_2^24"] = gbs(4 * n, time_region(lambda i: red(None, bufs[i % 8], cell), 16, stream))
+
+    def replayed(call, reps=5):
+        """ms per call of 16 calls captured once and replayed `reps` times; None if capture is refused."""
+        try:
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(16):
+                    call(i)
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / (16 * reps)
+        except Exception as exc:   # capture of a launch kind the driver refuses: keep the eager figure
+            torch.cuda.synchronize()
+            return None
+
+    for name, call, nbytes in (("scan_i32_exclusive_2^24", lambda i: scan(None, bufs[i % 8], outs[i % 8], temp), 8 * n),
+                               ("reduce_i32_sum_2^24", lambda i: red(None, bufs[i % 8], cell), 4 * n)):
+        eager_ms = time_region(call, 16, stream)
+        graph_ms = replayed(call)
+        entry = gbs(nbytes, graph_ms if graph_ms is not None else eager_ms)
+        entry["how"] = "16 calls captured in a CUDA graph and replayed" if graph_ms is not None else "eager calls"
+        entry["eager_ms"] = round(eager_ms, 4)
+        out[name] = entry
+    expect = torch.cumsum(bufs[3].to(torch.int64), 0)
+    assert int(outs[3][-1]) == int(((expect[-2] + 2 ** 31) % 2 ** 32) - 2 ** 31) and int(outs[3][0]) == 0, "scan result after replay"
     del bufs, outs
     # histogram of 2^28 float32 N(0,1) into 256 int32 bins
     n = 1 << 28

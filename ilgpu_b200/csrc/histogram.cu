@@ -265,6 +265,11 @@ extern "C" int b200alg_histogram(void *stream, const void *in, int64_t stride, i
     p.bins_d = (double)num_bins;
     p.bins_f = (float)num_bins;
     p.last = (int)(num_bins - 1);
+    // float input computes in float: a range that collapses or overflows there would put every
+    // element into an edge bin without a word
+    if (locator == B200ALG_LOCATOR_EQUAL_WIDTH_CLAMP && in_dtype == B200ALG_F32 &&
+        (!isfinite((float)lo) || !isfinite((float)hi) || !((float)hi > (float)lo) || !isfinite(p.scale_f) || !(p.scale_f > 0.0f)))
+        return B200ALG_INVALID_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     switch (in_dtype) {
     case B200ALG_I32: return dispatch_locator<int32_t>(s, in, stride, n, locator, p, bins, bin_dtype, overflow);

@@ -15,7 +15,10 @@ constexpr int kScanVecPerThread = 8;  // 8 x 16 bytes per thread -> 32 KB per ti
 constexpr int kScanMinTileElems = 2 * kScanVecPerThread * kScanThreads;  // tile of an 8-byte type
 
 // General variant (strided or unaligned views): one tile per block, handed out by an atomic
-// ticket, guarded element loads; thread t holds ITEMS consecutive elements of the tile.
+// ticket.  Thread t scans ITEMS consecutive elements of the tile, but global memory is touched
+// warp-striped (consecutive lanes, consecutive elements: for a strided view, addresses one
+// stride apart instead of ITEMS strides apart) and the warp transposes its chunk through
+// shared memory, padded by one slot per 32 so that both access patterns are conflict-free.
 template <typename T, int OP, bool INCLUSIVE>
 __global__ void __launch_bounds__(kScanThreads)
 scan_kernel(const T *in, int64_t in_stride, T *out, int64_t out_stride, int64_t n, const T *carry_in,
@@ -26,12 +29,14 @@ scan_kernel(const T *in, int64_t in_stride, T *out, int64_t out_stride, int64_t 
     constexpr int TILE = ITEMS * kScanThreads;
     struct Items { T t[ITEMS]; };
 
+    __shared__ T exchange[kScanWarps][32 * ITEMS + ITEMS];
     __shared__ T warp_total[kScanWarps];
     __shared__ T warp_excl[kScanWarps];
     __shared__ T s_prefix;
     __shared__ int s_tile;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    auto slot = [](int e) { return e + (e >> 5); };
     grid_dependency_wait();  // the descriptors and the ticket counter have been cleared
     if (tid == 0) s_tile = (int)atomicAdd(&hdr->reserved[0], 1u);
     __syncthreads();
@@ -40,11 +45,16 @@ scan_kernel(const T *in, int64_t in_stride, T *out, int64_t out_stride, int64_t 
     const int64_t remaining = n - base;
 
     Items it;
+    const int64_t warp_first = (int64_t)warp * (32 * ITEMS);  // first element of the warp's chunk inside the tile
 #pragma unroll
-    for (int k = 0; k < ITEMS; ++k) {
-        const int64_t idx = (int64_t)tid * ITEMS + k;
-        it.t[k] = idx < remaining ? in[(base + idx) * in_stride] : O::identity();
+    for (int j = 0; j < ITEMS; ++j) {
+        const int e = j * 32 + lane;
+        const int64_t idx = warp_first + e;
+        exchange[warp][slot(e)] = idx < remaining ? in[(base + idx) * in_stride] : O::identity();
     }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) it.t[k] = exchange[warp][slot(lane * ITEMS + k)];
 
     // Thread total -> warp scan -> block scan.
     T tsum = it.t[0];
@@ -132,10 +142,15 @@ scan_kernel(const T *in, int64_t in_stride, T *out, int64_t out_stride, int64_t 
         }
     }
 
+    __syncwarp();
 #pragma unroll
-    for (int k = 0; k < ITEMS; ++k) {
-        const int64_t idx = (int64_t)tid * ITEMS + k;
-        if (idx < remaining) out[(base + idx) * out_stride] = it.t[k];
+    for (int k = 0; k < ITEMS; ++k) exchange[warp][slot(lane * ITEMS + k)] = it.t[k];
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+        const int e = j * 32 + lane;
+        const int64_t idx = warp_first + e;
+        if (idx < remaining) out[(base + idx) * out_stride] = exchange[warp][slot(e)];
     }
 }
 

@@ -49,7 +49,8 @@ typedef enum { B200ALG_ADD = 0, B200ALG_MAX = 1, B200ALG_MIN = 2 } b200alg_op;
  * structs, IHistogramOperations.cs:19-78; a C ABI needs a closed set).
  *  EQUAL_WIDTH_CLAMP: t = (x - lo) * (num_bins / (hi - lo)) with the scale computed once
  *      in the input's floating type (double for integer inputs); bin = floor(t) clamped
- *      to [0, num_bins-1]; NaN -> bin 0.
+ *      to [0, num_bins-1]; NaN -> bin 0.  hi > lo must also hold, and the scale be finite,
+ *      in that type (B200ALG_INVALID_ARGUMENT otherwise).
  *  MODULO: the reference tests' ModuloBin*Operation (ILGPU.Algorithms.Tests/
  *      HistogramTests.tt:83-94): |x % num_bins| for integers, (int)|fmod(x, num_bins)|
  *      for floats. */

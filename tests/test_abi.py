@@ -63,6 +63,11 @@ def test_host_only_entry_points():
     assert L.b200alg_reduce(None, None, 1, 10, _native.I32, _native.ADD, None) == _native.INVALID_ARGUMENT
     assert L.b200alg_scan(None, None, 1, None, 1, 10, _native.I32, 0, 1, None, 0) == _native.INVALID_ARGUMENT
     assert L.b200alg_histogram(None, None, 1, 10, _native.F32, 0, 0.0, 1.0, None, 4, _native.I32, None) == _native.INVALID_ARGUMENT
+    # a range that is fine in double but collapses in float is refused for float input (pointers are
+    # only checked for null and alignment before that, never dereferenced on the host)
+    fake = ctypes.c_void_p(4096)
+    assert L.b200alg_histogram(None, fake, 1, 10, _native.F32, 0, 1.0, 1.0 + 1e-12, fake, 4, _native.I32, None) == _native.INVALID_ARGUMENT
+    assert L.b200alg_histogram(None, fake, 1, 10, _native.F32, 0, -1e300, 1e300, fake, 4, _native.I32, None) == _native.INVALID_ARGUMENT
 
 
 def test_missing_library_is_an_error(monkeypatch, tmp_path):
