@@ -261,12 +261,19 @@ template <typename K, typename XF = KeyXform<K>> struct RadixDigit {
     static constexpr bool kUsesIndex = false;
     XF xf;
     int shift;
-    __device__ __forceinline__ unsigned int operator()(K key, int64_t) const {
+    __device__ __forceinline__ unsigned int operator()(K key, int64_t, const unsigned char *) const {
         return (unsigned int)(xf(key) >> shift) & 0xFFu;
     }
 };
 template <typename K> struct SplitterBucket {
     static constexpr bool kUsesIndex = true;
+    static constexpr int kSmall = 7;  // up to this many splitters are compared without a loop
+    // The tables a block keeps in shared memory (16-byte aligned), by byte offset: splitter
+    // indices, transformed splitter keys, then (partition pass only) the destination pointers.
+    // They are addressed from the block's shared-memory base, so the kernel holds no pointer to
+    // them in registers.
+    static constexpr int kIndexAt = 0, kKeysAt = kRadix * 8, kKeyPointersAt = kRadix * 16, kValuePointersAt = kRadix * 24;
+    static constexpr int kTableBytes = kRadix * 32, kTableBytesWithoutPointers = kRadix * 16;
     KeyXform<K> xf;
     const K *splitter_keys;
     const int64_t *splitter_index;
@@ -277,35 +284,75 @@ template <typename K> struct SplitterBucket {
     // pass stores bucket b's elements at bucket_keys[b][0..count_b) instead of one output array.
     void *const *bucket_keys;
     void *const *bucket_values;
-    // Copies the splitters into shared memory (keys already transformed) and reads them from
-    // there afterwards; slots up to kSmall are padded with the largest key, which no key
-    // exceeds.  Call with all threads of the block, then synchronise.
-    static constexpr int kSmall = 7;  // up to this many splitters are compared without a loop
-    __device__ __forceinline__ void stage(K *shared_keys, int64_t *shared_index) {
+
+    // Fills the tables: keys already transformed, slots up to kSmall padded with the largest
+    // key, which no key exceeds.  Call with all threads of the block, then synchronise.
+    __device__ __forceinline__ void stage(unsigned char *tables, bool with_pointers) const {
+        K *keys = reinterpret_cast<K *>(tables + kKeysAt);
+        int64_t *index = reinterpret_cast<int64_t *>(tables + kIndexAt);
         for (int s = threadIdx.x; s < num_splitters; s += blockDim.x) {
-            shared_keys[s] = xf(splitter_keys[s]);
-            shared_index[s] = splitter_index[s];
+            keys[s] = xf(splitter_keys[s]);
+            index[s] = splitter_index[s];
         }
-        for (int s = num_splitters + threadIdx.x; s < kSmall; s += blockDim.x) shared_keys[s] = (K) ~(K)0;
-        splitter_keys = shared_keys;
-        splitter_index = shared_index;
+        for (int s = num_splitters + threadIdx.x; s < kSmall + 1; s += blockDim.x) keys[s] = (K) ~(K)0;
+        if (with_pointers && bucket_keys) {
+            void **kp = reinterpret_cast<void **>(tables + kKeyPointersAt);
+            void **vp = reinterpret_cast<void **>(tables + kValuePointersAt);
+            for (int s = threadIdx.x; s <= num_splitters; s += blockDim.x) {
+                kp[s] = bucket_keys[s];
+                if (bucket_values) vp[s] = bucket_values[s];
+            }
+        }
     }
-    __device__ __forceinline__ unsigned int operator()(K key, int64_t local_index) const {
+    static __device__ __forceinline__ void *key_pointer(const unsigned char *tables, unsigned int bucket) {
+        return reinterpret_cast<void *const *>(tables + kKeyPointersAt)[bucket];
+    }
+    static __device__ __forceinline__ void *value_pointer(const unsigned char *tables, unsigned int bucket) {
+        return reinterpret_cast<void *const *>(tables + kValuePointersAt)[bucket];
+    }
+    __device__ __forceinline__ unsigned int operator()(K key, int64_t local_index, const unsigned char *tables) const {
+        const K *sk = reinterpret_cast<const K *>(tables + kKeysAt);
         const K tk = xf(key);
         // The splitters ascend by (key, index): count those with a smaller key, then walk over
         // the (rare) ones with an equal key whose index does not exceed this element's.
         unsigned int b = 0;
-        if (num_splitters == 1) {
-            b = splitter_keys[0] < tk;
-        } else if (num_splitters <= kSmall) {
+        bool tie = false;
+        if (num_splitters <= kSmall) {
+            // eight slots, fetched with 16-byte loads from one address for the whole warp: a
+            // couple of shared-memory wavefronts per key instead of one per splitter; the
+            // branches below are uniform over the grid
+            constexpr int kVecs = (8 * (int)sizeof(K) + 15) / 16;
+            union { uint4 v[kVecs]; K k[16 / sizeof(K) > 8 ? 16 / sizeof(K) : 8]; } s;
+            const uint4 *from = reinterpret_cast<const uint4 *>(sk);
+            if (num_splitters <= 1) {
+                const K only = sk[0];
+                b = only < tk;
+                tie = only == tk;
+            } else if (num_splitters <= 3) {
+                s.v[0] = from[0];
+                if (sizeof(K) == 8) s.v[1 % kVecs] = from[1 % kVecs];
 #pragma unroll
-            for (int s = 0; s < kSmall; ++s) b += splitter_keys[s] < tk;
+                for (int j = 0; j < 3; ++j) {
+                    b += s.k[j] < tk;
+                    tie |= s.k[j] == tk;
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < kVecs; ++q) s.v[q] = from[q];
+#pragma unroll
+                for (int j = 0; j < kSmall; ++j) {
+                    b += s.k[j] < tk;
+                    tie |= s.k[j] == tk;
+                }
+            }
         } else {
-            for (int s = 0; s < num_splitters; ++s) b += splitter_keys[s] < tk;
+            for (int j = 0; j < num_splitters; ++j) b += sk[j] < tk;
+            tie = (int)b < num_splitters && sk[b] == tk;
         }
-        if ((int)b < num_splitters && splitter_keys[b] == tk) {
+        if (tie) {
+            const int64_t *si = reinterpret_cast<const int64_t *>(tables + kIndexAt);
             const int64_t gi = index_base + local_index;
-            while ((int)b < num_splitters && splitter_keys[b] == tk && splitter_index[b] <= gi) ++b;
+            while ((int)b < num_splitters && sk[b] == tk && si[b] <= gi) ++b;
         }
         return b;
     }
@@ -320,7 +367,8 @@ template <typename SW> struct IndexOf { using type = unsigned int; };
 template <> struct IndexOf<unsigned long long> { using type = unsigned long long; };
 
 // Full dense tiles are staged in shared memory by one bulk asynchronous copy (TMA, no
-// multicast) that is issued a tile ahead.
+// multicast) that is issued a tile ahead.  (Measured against plain loads of the next tile into
+// registers during the write-out: 1.22 ms against 1.31 ms for the 2^26-key sort.)
 constexpr bool kSortTma = true;
 constexpr int kLookWindow = 4;  // predecessors examined per look-back round (2 and 8 measured slower)
 // The digit passes are launched as programmatic dependents of one another: the blocks of the
@@ -343,7 +391,7 @@ struct OnesweepSmem {
     // when two blocks per SM would not fit otherwise, the masks live at the head of the
     // reorder buffer (and every warp clears its row again before it ranks the next tile).
     static constexpr size_t table_bytes = (size_t)WARPS * kRadix * 4;
-    static constexpr size_t fixed_bytes = kRadix * 16 + 256 + (KEEP_DIGITS ? (size_t)TILE + kRadix * 16 : 0) + 128;
+    static constexpr size_t fixed_bytes = kRadix * 16 + 256 + (KEEP_DIGITS ? (size_t)TILE + kRadix * 32 : 0) + 128;
     static constexpr bool MASKS_IN_SORTED =
         (size_t)TILE * SLOT >= table_bytes &&
         (size_t)TILE * SLOT + 2 * table_bytes + fixed_bytes + (size_t)TILE * sizeof(K) > 112 * 1024;
@@ -356,7 +404,8 @@ struct OnesweepSmem {
     static constexpr size_t off_context = off_misc + 128;   // the block's PassContext
     static constexpr size_t off_digits = off_context + 128;
     static constexpr size_t off_splitters = off_digits + (KEEP_DIGITS ? (size_t)TILE : 0);
-    static constexpr size_t off_stage = (off_splitters + (KEEP_DIGITS ? (size_t)kRadix * 16 : 0) + 127) / 128 * 128;
+    // splitters: 256 positions (8 bytes), 256 keys (8 bytes), 2 x 256 destination pointers
+    static constexpr size_t off_stage = (off_splitters + (KEEP_DIGITS ? (size_t)kRadix * 32 : 0) + 127) / 128 * 128;
     // The staging buffer of the bulk copies is dropped (keys are then loaded directly) where
     // it would cost the second block per SM.
     static constexpr size_t kTwoBlocksPerSm = 113 * 1024;
@@ -400,7 +449,7 @@ __device__ __forceinline__ int take_ticket(const PassContext<K, V, SW> &c, K *st
 // order: item i of lane l is element warp * 32 * ITEMS + i * 32 + l of the tile.
 template <typename K, typename V, typename SW, typename Digit, int THREADS, int ITEMS, bool FAST>
 __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int tile, unsigned int &bulk_phase,
-                                             const Digit &dg, unsigned char *smem_raw) {
+                                             K (&key)[ITEMS], bool &have_keys, const Digit &dg, unsigned char *smem_raw) {
     constexpr int WARPS = THREADS / 32;
     constexpr int TILE = THREADS * ITEMS;
     constexpr bool HAS_VALUES = ValueBytes<V>::value != 0;
@@ -440,12 +489,14 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
         }
     }
 
-    K key[ITEMS];
+    // The tile's keys: out of the staging buffer, or already in registers (requested while the
+    // block was finishing its previous tile), or loaded now.
     if (FAST && L::STAGED && c.bulk) {
         if (!mbar_wait(bar, bulk_phase) && lane == 0) atomicExch(&c.hdr->wait_limit_hit, 1u);
         bulk_phase ^= 1u;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) key[i] = stage[warp_base + i * 32];
+    } else if (have_keys) {
     } else if (FAST) {
         const K *p = c.src + tile_base + warp_base;
 #pragma unroll
@@ -457,8 +508,70 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
             key[i] = idx < c.n ? c.src[idx * c.src_stride] : K(0);
         }
     }
+    __syncwarp();
+
+    // Ranking inside the warp: for every item, the lanes that hold the same digit have to find
+    // each other.  Every lane ORs its bit into the digit's mask in the warp's table and reads
+    // the mask back after a warp barrier; the lowest lane of the mask adds the number of its
+    // lanes to the warp's count of that digit, clears the mask and hands the previous count to
+    // the others.  (Finding the peers with one warp vote per digit bit costs no shared memory
+    // but measured slower for any share of the items, and the hardware match instruction far
+    // slower.)  After the loop the warp's table holds its digit counts.
+    const unsigned int lt = lanemask_lt();
+    const unsigned int my_bit = 1u << lane;
+    const unsigned char *tables = smem_raw + L::off_splitters;  // of a SplitterBucket; unused otherwise
+    // A partition into up to eight buckets finds equal "digits" inside a warp by votes instead of
+    // the tables (with so few distinct values the tables serialise: all lanes of a bucket hit
+    // one word).  The buckets differ in their low three bits, the padding digit of a ragged
+    // tile from them in the fourth.  Uniform over the grid.
+    bool by_votes = false;
+    int votes = 0;
+    if constexpr (Digit::kUsesIndex) {
+        const int ns = dg.num_splitters;
+        by_votes = ns <= Digit::kSmall;
+        votes = !FAST ? 4 : (ns == 0 ? 0 : (ns == 1 ? 1 : (ns <= 3 ? 2 : 3)));
+    }
+    unsigned int packed[ITEMS];  // (rank among the warp's keys of that digit) << 8 | digit
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        unsigned int d;
+        if (FAST) {
+            d = dg(key[i], tile_base + warp_base + i * 32, tables);
+        } else {
+            const int local = warp_base + i * 32;
+            d = local < valid ? dg(key[i], tile_base + local, tables) : 0xFFu;  // padding ranks behind every real key
+        }
+        unsigned int peers;
+        if (by_votes) {
+            peers = 0xffffffffu;
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                if (b < votes) {
+                    const bool bit = ((d >> b) & 1u) != 0u;
+                    const unsigned int m = __ballot_sync(0xffffffffu, bit);
+                    peers &= bit ? m : ~m;
+                }
+            }
+        } else {
+            atomicOr(&my_mask[d], my_bit);
+            __syncwarp();
+            peers = my_mask[d];
+            __syncwarp();
+        }
+        unsigned int count = 0u;
+        if ((peers & lt) == 0u) {  // lowest lane with this digit
+            count = atomicAdd(&my_count[d], (unsigned int)__popc(peers));
+            if (!by_votes) my_mask[d] = 0u;
+        }
+        __syncwarp();  // the counts advance item by item
+        count = __shfl_sync(0xffffffffu, count, __ffs(peers) - 1);
+        packed[i] = ((count + (unsigned int)__popc(peers & lt)) << 8) | d;
+    }
+    __syncthreads();  // A: the tables are complete; every thread has its keys out of the staging buffer
+
+    // The values are not held during the ranking: sixteen more live registers there spill.
     V val[HAS_VALUES ? ITEMS : 1];
-    if constexpr (HAS_VALUES) {  // requested now, needed after the ranking
+    if constexpr (HAS_VALUES) {  // requested now, in flight while the digit threads work, needed for the reorder
         bool from_index = false;
         if constexpr (sizeof(V) <= 8) from_index = c.value_seq != kSeqNone;
         if (from_index) {
@@ -474,41 +587,6 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
             }
         }
     }
-    __syncwarp();
-
-    // Ranking inside the warp: for every item, the lanes that hold the same digit have to find
-    // each other.  Every lane ORs its bit into the digit's mask in the warp's table and reads
-    // the mask back after a warp barrier; the lowest lane of the mask adds the number of its
-    // lanes to the warp's count of that digit, clears the mask and hands the previous count to
-    // the others.  (Finding the peers with one warp vote per digit bit costs no shared memory
-    // but measured slower for any share of the items, and the hardware match instruction far
-    // slower.)  After the loop the warp's table holds its digit counts.
-    const unsigned int lt = lanemask_lt();
-    const unsigned int my_bit = 1u << lane;
-    unsigned int packed[ITEMS];  // (rank among the warp's keys of that digit) << 8 | digit
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-        unsigned int d;
-        if (FAST) {
-            d = dg(key[i], tile_base + warp_base + i * 32);
-        } else {
-            const int local = warp_base + i * 32;
-            d = local < valid ? dg(key[i], tile_base + local) : 0xFFu;  // padding ranks behind every real key
-        }
-        atomicOr(&my_mask[d], my_bit);
-        __syncwarp();
-        const unsigned int peers = my_mask[d];
-        __syncwarp();
-        unsigned int count = 0u;
-        if ((peers & lt) == 0u) {  // lowest lane with this digit
-            count = atomicAdd(&my_count[d], (unsigned int)__popc(peers));
-            my_mask[d] = 0u;
-        }
-        __syncwarp();  // the counts advance item by item
-        count = __shfl_sync(0xffffffffu, count, __ffs(peers) - 1);
-        packed[i] = ((count + (unsigned int)__popc(peers & lt)) << 8) | d;
-    }
-    __syncthreads();  // A: the tables are complete; every thread has its keys out of the staging buffer
 
     if (tid == THREADS - 1) misc[8] = (unsigned int)take_ticket<K, V, SW, TILE, L::STAGED>(c, stage, bar);
 
@@ -555,9 +633,34 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
         const unsigned int d = packed[i] & 0xFFu;
         const unsigned int slot = (packed[i] >> 8) + my_count[d];
         skeys[slot] = key[i];
-        if constexpr (Digit::kUsesIndex) sdigit[slot] = (unsigned char)d;
+        if constexpr (Digit::kUsesIndex) {
+            if (dg.num_splitters > Digit::kSmall) sdigit[slot] = (unsigned char)d;  // few buckets: found again from the slot
+        }
         if constexpr (L::SPLIT) svals[slot] = val[i];
         if constexpr (SECOND_ROUND) pos[i] = slot;
+    }
+    // The key registers are free again.  Unless the next tile arrives through the staging
+    // buffer, request its keys now: the loads are in flight during the look-back and the
+    // write-out.
+    {
+        const int next = (int)misc[8];
+        const bool next_full = (int64_t)(next + 1) * TILE <= c.n;
+        have_keys = false;
+        if (next < c.num_tiles && !(L::STAGED && c.bulk && next_full)) {
+            const int64_t next_base = (int64_t)next * TILE;
+            if (c.dense && next_full) {
+                const K *p = c.src + next_base + warp_base;
+#pragma unroll
+                for (int i = 0; i < ITEMS; ++i) key[i] = p[i * 32];
+            } else {
+#pragma unroll
+                for (int i = 0; i < ITEMS; ++i) {
+                    const int64_t idx = next_base + warp_base + i * 32;
+                    key[i] = idx < c.n ? c.src[idx * c.src_stride] : K(0);
+                }
+            }
+            have_keys = true;
+        }
     }
     // Decoupled look-back by the last 256 threads, one digit per thread, kLookWindow
     // predecessors per round (their loads are independent, so a round costs one trip to L2).
@@ -602,35 +705,62 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
     }
     __syncthreads();  // D
 
-    Idx out_idx[SECOND_ROUND ? ITEMS : 1];
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-        const int p = tid + i * THREADS;
-        if (FAST || p < valid) {
-            const K k = skeys[p];
-            unsigned int d;
-            if constexpr (Digit::kUsesIndex) d = sdigit[p]; else d = dg(k, 0);
-            const Idx at = bin_goff[d] + (Idx)p;
-            if constexpr (SECOND_ROUND) out_idx[i] = at;
-            bool stored = false;
-            if constexpr (Digit::kUsesIndex) {
-                if (dg.bucket_keys) {  // plain stores, possibly over NVLink into a peer's receive buffer
-                    reinterpret_cast<K *>(dg.bucket_keys[d])[at] = k;
-                    stored = true;
-                }
-            }
-            if (!stored) {
-                if (FAST) c.dst[at] = k; else c.dst[(int64_t)at * c.dst_stride] = k;
-            }
-            if constexpr (L::SPLIT) {  // the value travels with its key
-                bool vstored = false;
-                if constexpr (Digit::kUsesIndex) {
-                    if (dg.bucket_values) {
-                        reinterpret_cast<V *>(dg.bucket_values[d])[at] = svals[p];
-                        vstored = true;
+    // With few buckets (the ranks of one box) the write-out goes bucket by bucket: a bucket is a
+    // run of consecutive slots with one destination, so nothing is looked up per element.
+    bool few_buckets = false;
+    if constexpr (Digit::kUsesIndex) few_buckets = dg.num_splitters <= Digit::kSmall;
+    auto store_runs = [&](bool keys_too, bool values_too) {
+        if constexpr (Digit::kUsesIndex) {
+            const bool scattered = dg.bucket_keys != nullptr;
+            for (int b = 0; b <= dg.num_splitters; ++b) {
+                const int lo = (int)bin_excl[b], hi = (int)bin_excl[b + 1];  // padding keys rank last
+                const Idx g = bin_goff[b];
+                K *kd = scattered ? reinterpret_cast<K *>(Digit::key_pointer(tables, b)) : c.dst;
+                const int64_t ks = scattered ? 1 : c.dst_stride;
+                if (keys_too)
+                    for (int p = lo + tid; p < hi; p += THREADS) kd[(int64_t)(g + (Idx)p) * ks] = skeys[p];
+                if constexpr (!std::is_same<V, NoValue>::value) {
+                    if (values_too) {
+                        V *vd = scattered && dg.bucket_values ? reinterpret_cast<V *>(Digit::value_pointer(tables, b)) : c.vdst;
+                        for (int p = lo + tid; p < hi; p += THREADS) vd[g + (Idx)p] = svals[p];
                     }
                 }
-                if (!vstored) c.vdst[at] = svals[p];
+            }
+        }
+    };
+    Idx out_idx[SECOND_ROUND ? ITEMS : 1];
+    if (few_buckets) {
+        store_runs(true, L::SPLIT);
+    } else {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int p = tid + i * THREADS;
+            if (FAST || p < valid) {
+                const K k = skeys[p];
+                unsigned int d;
+                if constexpr (Digit::kUsesIndex) d = sdigit[p]; else d = dg(k, 0, tables);
+                const Idx at = bin_goff[d] + (Idx)p;
+                if constexpr (SECOND_ROUND) out_idx[i] = at;
+                bool stored = false;
+                if constexpr (Digit::kUsesIndex) {
+                    if (dg.bucket_keys) {  // plain stores, possibly over NVLink into a peer's receive buffer
+                        reinterpret_cast<K *>(Digit::key_pointer(tables, d))[at] = k;
+                        stored = true;
+                    }
+                }
+                if (!stored) {
+                    if (FAST) c.dst[at] = k; else c.dst[(int64_t)at * c.dst_stride] = k;
+                }
+                if constexpr (L::SPLIT) {  // the value travels with its key
+                    bool vstored = false;
+                    if constexpr (Digit::kUsesIndex) {
+                        if (dg.bucket_values) {
+                            reinterpret_cast<V *>(Digit::value_pointer(tables, d))[at] = svals[p];
+                            vstored = true;
+                        }
+                    }
+                    if (!vstored) c.vdst[at] = svals[p];
+                }
             }
         }
     }
@@ -643,18 +773,22 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
             if (FAST || local < valid) svals[pos[i]] = val[i];
         }
         __syncthreads();
+        if (few_buckets) {
+            store_runs(false, true);
+        } else {
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) {
-            const int p = tid + i * THREADS;
-            if (FAST || p < valid) {
-                bool stored = false;
-                if constexpr (Digit::kUsesIndex) {
-                    if (dg.bucket_values) {
-                        reinterpret_cast<V *>(dg.bucket_values[sdigit[p]])[out_idx[i]] = svals[p];
-                        stored = true;
+            for (int i = 0; i < ITEMS; ++i) {
+                const int p = tid + i * THREADS;
+                if (FAST || p < valid) {
+                    bool stored = false;
+                    if constexpr (Digit::kUsesIndex) {
+                        if (dg.bucket_values) {
+                            reinterpret_cast<V *>(Digit::value_pointer(tables, sdigit[p]))[out_idx[i]] = svals[p];
+                            stored = true;
+                        }
                     }
+                    if (!stored) c.vdst[out_idx[i]] = svals[p];
                 }
-                if (!stored) c.vdst[out_idx[i]] = svals[p];
             }
         }
     }
@@ -675,14 +809,13 @@ onesweep_kernel(SortBuffers<K, V> io, int pass, Digit dg, TempHeader *hdr, const
     using L = OnesweepSmem<K, V, Digit::kUsesIndex, THREADS, ITEMS>;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    if (kSortPdl) {
-        grid_dependency_release();  // the next kernel of the call may take the SMs this one leaves
-        {   // meanwhile: the part of the set-up that reads nothing
-            uint4 *zm = reinterpret_cast<uint4 *>(smem_raw + L::off_mask);
-            for (int i = threadIdx.x; i < (THREADS / 32) * kRadix / 4; i += THREADS) zm[i] = make_uint4(0u, 0u, 0u, 0u);
-        }
-        grid_dependency_wait();     // everything the kernels before this one wrote is visible from here on
+    if (kSortPdl) grid_dependency_release();  // the next kernel of the call may take the SMs this one leaves
+    {   // The part of the set-up that reads nothing: the lane masks of the ranking tables start at
+        // zero and are left at zero by every item.
+        uint4 *zm = reinterpret_cast<uint4 *>(smem_raw + L::off_mask);
+        for (int i = threadIdx.x; i < (THREADS / 32) * kRadix / 4; i += THREADS) zm[i] = make_uint4(0u, 0u, 0u, 0u);
     }
+    if (kSortPdl) grid_dependency_wait();  // everything the kernels before this one wrote is visible from here on
     if (hdr->reserved[kCtlSkip + pass]) return;
     // The pass description lives in shared memory: a dozen pointers that would otherwise sit
     // in registers for the whole kernel.
@@ -720,22 +853,19 @@ onesweep_kernel(SortBuffers<K, V> io, int pass, Digit dg, TempHeader *hdr, const
         misc[8] = (unsigned int)take_ticket<K, V, SW, TILE, L::STAGED>(c, reinterpret_cast<K *>(smem_raw + L::off_stage), bar);
     }
     if constexpr (Digit::kUsesIndex)
-        dg.stage(reinterpret_cast<K *>(smem_raw + L::off_splitters + kRadix * 8),
-                 reinterpret_cast<int64_t *>(smem_raw + L::off_splitters));
-    {   // the lane masks of the ranking tables start at zero and are left at zero by every item
-        uint4 *zm = reinterpret_cast<uint4 *>(smem_raw + L::off_mask);
-        for (int i = threadIdx.x; i < (THREADS / 32) * kRadix / 4; i += THREADS) zm[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
+        dg.stage(smem_raw + L::off_splitters, true);
     __syncthreads();
     int tile = (int)misc[8];
     __syncthreads();  // misc[8] is written again during the first tile
     const bool dense = io.stride == 1;
     unsigned int bulk_phase = 0u;
+    K key[ITEMS];
+    bool have_keys = false;
     while (tile < num_tiles) {
         if (dense && (int64_t)(tile + 1) * TILE <= n)
-            tile = onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, true>(c, tile, bulk_phase, dg, smem_raw);
+            tile = onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, true>(c, tile, bulk_phase, key, have_keys, dg, smem_raw);
         else
-            tile = onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, false>(c, tile, bulk_phase, dg, smem_raw);
+            tile = onesweep_tile<K, V, SW, Digit, THREADS, ITEMS, false>(c, tile, bulk_phase, key, have_keys, dg, smem_raw);
     }
 }
 
@@ -952,9 +1082,8 @@ template <typename K>
 __global__ void __launch_bounds__(256)
 bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K> dg, unsigned long long *ghist) {
     __shared__ unsigned int sh[8][kRadix];
-    __shared__ K staged_keys[kRadix];
-    __shared__ int64_t staged_index[kRadix];
-    dg.stage(staged_keys, staged_index);
+    __shared__ __align__(16) unsigned char tables[SplitterBucket<K>::kTableBytesWithoutPointers];
+    dg.stage(tables, false);
     for (int i = threadIdx.x; i < 8 * kRadix; i += 256) (&sh[0][0])[i] = 0u;
     __syncthreads();
     unsigned int *mine = sh[threadIdx.x >> 5];
@@ -984,9 +1113,9 @@ bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K>
             a.u = __ldcs(vin + v);
             b.u = __ldcs(vin + v + step);
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(a.k[k], head + v * VEC + k));
+            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(a.k[k], head + v * VEC + k, tables));
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(b.k[k], head + (v + step) * VEC + k));
+            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(b.k[k], head + (v + step) * VEC + k, tables));
             pending += 2 * VEC;
             if (pending > 255 - 2 * VEC) flush();
         }
@@ -994,15 +1123,15 @@ bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K>
             Pack a;
             a.u = __ldcs(vin + v);
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(a.k[k], head + v * VEC + k));
+            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(a.k[k], head + v * VEC + k, tables));
             pending += VEC;
             if (pending > 255 - 2 * VEC) flush();
         }
         flush();
         if (blockIdx.x == 0) {  // the unaligned ends: fewer than 16 bytes each
-            if (threadIdx.x < head) total[dg(keys[threadIdx.x], threadIdx.x)] += 1u;
+            if (threadIdx.x < head) total[dg(keys[threadIdx.x], threadIdx.x, tables)] += 1u;
             const int64_t j = tail + threadIdx.x;
-            if (j < n) total[dg(keys[j], j)] += 1u;
+            if (j < n) total[dg(keys[j], j, tables)] += 1u;
         }
 #pragma unroll
         for (int b = 0; b < 8; ++b) {
@@ -1012,7 +1141,7 @@ bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K>
             if ((threadIdx.x & 31) == 0 && t) mine[b] = t;
         }
     } else {
-        for (int64_t i = gtid; i < n; i += step) atomicAdd(mine + dg(keys[i], i), 1u);
+        for (int64_t i = gtid; i < n; i += step) atomicAdd(mine + dg(keys[i], i, tables), 1u);
     }
     __syncthreads();
     unsigned int c = 0;

@@ -87,3 +87,22 @@ def test_strided_input(accelerator):
     bins = torch.zeros(64, dtype=torch.uint32, device="cuda")
     accelerator.HistogramUnchecked(None, view, bins, EqualWidthClampLocator(-3.0, 3.0))
     np.testing.assert_array_equal(to_host(bins), expected)
+
+
+def test_float_bins_beyond_2_pow_24_the_stated_exception(accelerator):
+    """The one stated parity exception of the histogram.  The reference adds 1.0f per element, so
+    a float bin stops growing at 2^24 (16777216.0f + 1.0f == 16777216.0f); here a block's count
+    goes in with one atomic add, so the bin keeps counting.  Below 2^24 the two agree exactly
+    (the cases above); this test pins the behaviour beyond it: 2^25 elements into one float bin
+    give exactly 2^25, the overflow flag stays clear, and an int32 bin next to it agrees."""
+    n = 1 << 25
+    x = torch.zeros(n, dtype=torch.int32, device="cuda")          # modulo locator: everything lands in bin 0
+    float_bins = torch.zeros(4, dtype=torch.float32, device="cuda")
+    int_bins = torch.zeros(4, dtype=torch.int32, device="cuda")
+    overflow = torch.zeros(1, dtype=torch.int32, device="cuda")
+    accelerator.Histogram(None, x, float_bins, overflow, ModuloLocator())
+    accelerator.Histogram(None, x, int_bins, overflow, ModuloLocator())
+    assert float(float_bins[0]) == float(n) and float(float_bins[1:].abs().sum()) == 0.0
+    assert int(int_bins[0]) == n
+    assert int(overflow[0]) == 0
+    assert np.float32(2 ** 24) + np.float32(1) == np.float32(2 ** 24)   # where the reference's bin would have stopped
