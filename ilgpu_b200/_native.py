@@ -38,6 +38,7 @@ SIGNATURES = {
     "b200alg_bucket_partition": (_int, [_vp, _vp, _vp, _i64, _int, _int, _int, _vp, _vp, _int, _i64, _vp, _vp, _vp, _vp, _i64]),
     "b200alg_bucket_count": (_int, [_vp, _vp, _i64, _int, _int, _vp, _vp, _int, _i64, _vp, _vp, _i64]),
     "b200alg_bucket_scatter": (_int, [_vp, _vp, _vp, _i64, _int, _int, _int, _vp, _vp, _int, _i64, _vp, _vp, _vp, _i64]),
+    "b200alg_select_splitters": (_int, [_vp, _vp, _vp, _i64, _vp, _int, _int, _int, _vp, _vp, _vp, _i64]),
     "b200alg_scan_temp_bytes": (_int, [_int, _i64, ctypes.POINTER(_i64)]),
     "b200alg_scan": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _int, _int, _int, _vp, _i64]),
     "b200alg_scan_carry": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _int, _int, _int, _vp, _vp, _i64]),

@@ -68,8 +68,8 @@ struct b200alg_comm {
     void **d_peer_recv = nullptr;           // device copies of the two tables
     unsigned int **d_peer_flags = nullptr;
     unsigned char *scratch = nullptr;       // device: sample arrays, partition temp, sort temp, histogram bins
-    int64_t off_samples_send = 0, off_samples_all = 0, off_sample_keys = 0, off_sample_index = 0, off_sorted_keys = 0,
-            off_sorted_index = 0, off_partition_temp = 0, partition_temp_bytes = 0, off_sort_temp = 0, sort_temp_bytes = 0,
+    int64_t off_samples_send = 0, off_samples_all = 0, off_sample_keys = 0, off_sample_index = 0,
+            off_partition_temp = 0, partition_temp_bytes = 0, off_sort_temp = 0, sort_temp_bytes = 0,
             off_sink = 0, off_bins = 0, scratch_bytes = 0;
 };
 
@@ -225,22 +225,6 @@ __global__ void collect_samples_kernel(const long long *all, int ranks, K *sampl
     }
 }
 
-template <typename K>
-__global__ void pick_splitters_kernel(const K *sorted_keys, const long long *sorted_index, const long long *count, int ranks,
-                                      K *splitter_keys, long long *splitter_index) {
-    const int j = threadIdx.x + 1;
-    if (j >= ranks) return;
-    const long long m = *count;
-    if (m <= 0) {
-        splitter_keys[j - 1] = (K)0;
-        splitter_index[j - 1] = 0;
-        return;
-    }
-    const long long at = ((long long)j * m) / ranks;
-    splitter_keys[j - 1] = sorted_keys[at];
-    splitter_index[j - 1] = sorted_index[at];
-}
-
 // From the matrix of bucket sizes (matrix[src][dst], the same on every rank): where this rank's
 // buckets start inside the owners' receive buffers, how much this rank receives, and whether
 // every receive buffer is large enough.  If one is not, every rank sends its buckets into a
@@ -303,15 +287,13 @@ static int finish_comm(b200alg_comm *c, int64_t sort_capacity, cudaStream_t s) {
     c->off_samples_all = take(G * msg_words * 8);
     c->off_sample_keys = take(total_samples * 8);
     c->off_sample_index = take(total_samples * 8);
-    c->off_sorted_keys = take(total_samples * 8);
-    c->off_sorted_index = take(total_samples * 8);
     c->off_bins = take(1 << 20);  // local bin counts of the histogram (up to 128 Ki 8-byte bins)
     int64_t need = 0;
     const int64_t cap1 = c->capacity < 1 ? 1 : c->capacity;
     {
-        int64_t a = 0, b = 0;
+        int64_t a = 0;
         if (b200alg_radix_sort_temp_bytes(B200ALG_U64, cap1, 8, &a) != B200ALG_OK) return B200ALG_INVALID_ARGUMENT;
-        if (b200alg_radix_sort_temp_bytes(B200ALG_U64, total_samples, 8, &b) != B200ALG_OK) return B200ALG_INVALID_ARGUMENT;
+        const int64_t b = total_samples * 4;  // the ranks of the samples while the splitters are picked
         need = a > b ? a : b;
     }
     c->sort_temp_bytes = need;
@@ -412,8 +394,6 @@ static int sort_mg_typed(b200alg_comm *c, cudaStream_t s, const void *keys, cons
     long long *all = (long long *)(sc + c->off_samples_all);
     K *sample_keys = (K *)(sc + c->off_sample_keys);
     long long *sample_index = (long long *)(sc + c->off_sample_index);
-    K *sorted_keys = (K *)(sc + c->off_sorted_keys);
-    long long *sorted_index = (long long *)(sc + c->off_sorted_index);
     const int64_t msg_words = 2 * kSamplesPerRank + 1;
     const int64_t total_samples = (int64_t)G * kSamplesPerRank;
 
@@ -423,15 +403,12 @@ static int sort_mg_typed(b200alg_comm *c, cudaStream_t s, const void *keys, cons
     B200ALG_NCCL_TRY(c, ncclAllGather(msg, all, (size_t)msg_words, ncclInt64, c->nccl, s));
     collect_samples_kernel<K><<<G, 256, 0, s>>>(all, G, sample_keys, sample_index, &st->sample_count);
     B200ALG_LAUNCH_CHECK();
-    // blocks lie in rank order and positions ascend inside a block, so a stable sort by key
-    // orders the (key, position) pairs
-    int rc = b200alg_radix_sort_out_of_place(s, sample_keys, sample_index, sorted_keys, sorted_index, total_samples,
-                                             (const int64_t *)&st->sample_count, key_dtype, 8, order, sc + c->off_sort_temp,
-                                             c->sort_temp_bytes);
+    // blocks lie in rank order and positions ascend inside a block, so slot order breaks ties the
+    // way positions would; the splitters are the pairs of ranks j * count / G, found by counting
+    int rc = b200alg_select_splitters(s, sample_keys, (const int64_t *)sample_index, total_samples,
+                                      (const int64_t *)&st->sample_count, key_dtype, order, G - 1, st->splitter_keys,
+                                      (int64_t *)st->splitter_index, sc + c->off_sort_temp, c->sort_temp_bytes);
     if (rc != B200ALG_OK) return rc;
-    pick_splitters_kernel<K><<<1, 32, 0, s>>>(sorted_keys, sorted_index, &st->sample_count, G, (K *)st->splitter_keys,
-                                              st->splitter_index);
-    B200ALG_LAUNCH_CHECK();
 
     // 2. bucket sizes of this shard, and everybody's
     const long long base = (long long)c->rank << kRankShift;

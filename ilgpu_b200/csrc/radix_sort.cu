@@ -1457,6 +1457,100 @@ extern "C" int b200alg_bucket_partition(void *stream, const void *keys, const vo
     return B200ALG_UNSUPPORTED;
 }
 
+// ---- 6. splitters out of a sample, without sorting it --------------------------------------
+// Pair t's rank is the number of pairs in front of it in the order (transformed key, slot):
+// what a stable sort by key would give.  A block holds 256 pairs and counts against a slab of
+// kSelectSlab pairs in shared memory; the partial ranks meet in global memory.
+constexpr int kSelectSlab = 1024;
+constexpr int64_t kSelectMax = 1 << 16;
+
+template <typename K>
+__global__ void __launch_bounds__(256)
+sample_rank_kernel(const K *__restrict__ keys, const long long *m_device, int64_t max_m, KeyXform<K> xf, unsigned int *ranks) {
+    __shared__ K slab[kSelectSlab];
+    long long m = *m_device;
+    m = m < 0 ? 0 : (m > max_m ? max_m : m);
+    const int64_t first = (int64_t)blockIdx.x * 256, slab_first = (int64_t)blockIdx.y * kSelectSlab;
+    if (first >= m || slab_first >= m) return;
+    const int len = (int)(m - slab_first < kSelectSlab ? m - slab_first : kSelectSlab);
+    for (int j = threadIdx.x; j < len; j += 256) slab[j] = xf(keys[slab_first + j]);
+    __syncthreads();
+    const int64_t t = first + threadIdx.x;
+    if (t >= m) return;
+    const K mine = xf(keys[t]);
+    // slots of the slab in front of t break ties in their favour, the others do not
+    const int split = (int)(t - slab_first < 0 ? 0 : (t - slab_first > len ? len : t - slab_first));
+    unsigned int r = 0;
+    for (int j = 0; j < split; ++j) r += slab[j] <= mine;
+    for (int j = split; j < len; ++j) r += slab[j] < mine;
+    if (r) atomicAdd(&ranks[t], r);
+}
+
+template <typename K>
+__global__ void __launch_bounds__(256)
+sample_pick_kernel(const K *__restrict__ keys, const int64_t *__restrict__ index, const long long *m_device, int64_t max_m,
+                   const unsigned int *ranks, int num_picks, K *out_keys, int64_t *out_index) {
+    long long m = *m_device;
+    m = m < 0 ? 0 : (m > max_m ? max_m : m);
+    const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (m == 0) {
+        if (t < num_picks) {
+            out_keys[t] = (K)0;
+            out_index[t] = 0;
+        }
+        return;
+    }
+    if (t >= m) return;
+    const long long r = ranks[t];
+    for (int j = 0; j < num_picks; ++j) {
+        if (((long long)(j + 1) * m) / (num_picks + 1) == r) {
+            out_keys[j] = keys[t];
+            out_index[j] = index[t];
+        }
+    }
+}
+
+template <typename K>
+static int select_typed(cudaStream_t s, const void *keys, const int64_t *index, int64_t max_m, const long long *m_device,
+                        uint64_t xn, uint64_t xp, int num_picks, void *out_keys, int64_t *out_index, void *temp) {
+    B200ALG_CUDA_TRY(cudaMemsetAsync(temp, 0, (size_t)max_m * 4, s));
+    const dim3 grid((unsigned)ceil_div(max_m, 256), (unsigned)ceil_div(max_m, kSelectSlab));
+    sample_rank_kernel<K><<<grid, 256, 0, s>>>((const K *)keys, m_device, max_m, KeyXform<K>{(K)xn, (K)xp}, (unsigned int *)temp);
+    B200ALG_LAUNCH_CHECK();
+    const int64_t threads = max_m > num_picks ? max_m : num_picks;
+    sample_pick_kernel<K><<<(unsigned)ceil_div(threads, 256), 256, 0, s>>>((const K *)keys, index, m_device, max_m,
+                                                                          (const unsigned int *)temp, num_picks, (K *)out_keys,
+                                                                          out_index);
+    B200ALG_LAUNCH_CHECK();
+    return B200ALG_OK;
+}
+
+extern "C" int b200alg_select_splitters(void *stream, const void *keys, const int64_t *index, int64_t max_m,
+                                        const int64_t *m_device, int key_dtype, int order, int num_picks, void *out_keys,
+                                        int64_t *out_index, void *temp, int64_t temp_bytes) {
+    if (!keys || !index || !m_device || !temp || max_m < 1 || num_picks < 0 || num_picks > 254) return B200ALG_INVALID_ARGUMENT;
+    if (num_picks && (!out_keys || !out_index)) return B200ALG_INVALID_ARGUMENT;
+    if (max_m > kSelectMax) return B200ALG_TOO_LARGE;
+    const int kb = dtype_bytes(key_dtype);
+    if (kb == 0) return B200ALG_UNSUPPORTED;
+    if (((uintptr_t)keys % kb) || ((uintptr_t)out_keys % kb) || ((uintptr_t)temp % 4) || ((uintptr_t)index % 8) ||
+        ((uintptr_t)out_index % 8) || ((uintptr_t)m_device % 8))
+        return B200ALG_MISALIGNED;
+    if (temp_bytes < max_m * 4) return B200ALG_TEMP_TOO_SMALL;
+    uint64_t xn, xp;
+    if (!key_xform_constants(key_dtype, order, xn, xp)) return B200ALG_UNSUPPORTED;
+    if (num_picks == 0) return B200ALG_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long *m = (const long long *)m_device;
+    switch (kb) {
+    case 1: return select_typed<uint8_t>(s, keys, index, max_m, m, xn, xp, num_picks, out_keys, out_index, temp);
+    case 2: return select_typed<uint16_t>(s, keys, index, max_m, m, xn, xp, num_picks, out_keys, out_index, temp);
+    case 4: return select_typed<uint32_t>(s, keys, index, max_m, m, xn, xp, num_picks, out_keys, out_index, temp);
+    case 8: return select_typed<uint64_t>(s, keys, index, max_m, m, xn, xp, num_picks, out_keys, out_index, temp);
+    }
+    return B200ALG_UNSUPPORTED;
+}
+
 extern "C" int b200alg_bucket_count(void *stream, const void *keys, int64_t n, int key_dtype, int order,
                                     const void *splitter_keys, const int64_t *splitter_index, int num_splitters,
                                     int64_t index_base, int64_t *bucket_counts, void *temp, int64_t temp_bytes) {

@@ -120,6 +120,20 @@ class NativeEngine:
                 splitter_keys.numel(), int(index_base), _ptr(counts), _ptr(temp), temp.numel() * 4))
         return counts
 
+    def select_splitters(self, sample_keys, sample_index, count, op: RadixSortOperation, num_picks: int):
+        """The pairs of ranks (j + 1) * count / (num_picks + 1) among the first `count` (a device
+        int64) samples, in the order a stable sort of the keys would give, without sorting."""
+        max_m = sample_keys.numel()
+        out_keys = self.empty(num_picks, sample_keys.dtype)
+        out_index = self.empty(num_picks, torch.int64)
+        temp = self._temp("select", max_m)
+        with self.acc.Bind():
+            B200AlgException.ThrowIfFailed(self.acc.L.b200alg_select_splitters(
+                _stream_ptr(None), _ptr(sample_keys), _ptr(sample_index), max_m, _ptr(count),
+                dtype_code(sample_keys.dtype), N.SORT_DESCENDING if op.descending else 0, int(num_picks),
+                _ptr(out_keys), _ptr(out_index), _ptr(temp), temp.numel() * 4))
+        return out_keys, out_index
+
     def bucket_scatter(self, keys, values, op: RadixSortOperation, splitter_keys, splitter_index, index_base: int,
                        key_pointers: list[int], value_pointers: list[int] | None) -> None:
         """Stores bucket b of this shard at key_pointers[b] (an address that may lie in a peer

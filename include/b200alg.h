@@ -145,6 +145,16 @@ int b200alg_bucket_scatter(void *stream, const void *keys, const void *values, i
                            void *const *bucket_key_ptrs, void *const *bucket_value_ptrs, void *temp,
                            int64_t temp_bytes);
 
+/* Splitters out of a sample of (key, index) pairs without sorting it: for j in [0, num_picks)
+ * the pair of rank ((j + 1) * m) / (num_picks + 1) in the order a stable sort of the keys with
+ * `order` would give (equal keys keep their slot order), raw key bits and index.  m is read on
+ * the device from m_device[0] and clamped to [0, max_m]; m == 0 yields zeros.  Every pair counts
+ * the pairs in front of it (quadratic: max_m <= 65536).  temp: max_m * 4 bytes, 4-byte aligned.
+ * No counterpart in the reference; the multi-GPU sort picks its splitters with it. */
+int b200alg_select_splitters(void *stream, const void *keys, const int64_t *index, int64_t max_m,
+                             const int64_t *m_device, int key_dtype, int order, int num_picks,
+                             void *out_keys, int64_t *out_index, void *temp, int64_t temp_bytes);
+
 /* ---- scan -------------------------------------------------------------------------
  * Replaces the lambda of CreateScan (ScanExtensions.cs:930-959 -> SinglePassScanKernel
  * :530-706).  out[i*out_stride] = fold(op, in[0..i]) (inclusive) or fold(op, in[0..i-1])

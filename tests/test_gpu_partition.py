@@ -115,3 +115,41 @@ def test_partition_count_scatter(accelerator, tname, np_t, num_splitters, direct
     # keys only
     out_keys, _, counts = eng.partition(dkeys, None, op, splitter_keys, splitter_index, base)
     assert np.array_equal(bits(out_keys), want_bits)
+
+
+@pytest.mark.parametrize("tname,np_t", [("UInt32", np.uint32), ("Int32", np.int32), ("Float", np.float32),
+                                         ("UInt64", np.uint64), ("Double", np.float64)])
+@pytest.mark.parametrize("direction", ["Ascending", "Descending"])
+@pytest.mark.parametrize("slots,count,picks,distinct", [(4096, 4096, 1, 0), (4096, 4096, 7, 5), (6144, 4100, 3, 0),
+                                                        (2048, 5, 7, 2), (2048, 0, 3, 0), (16384, 16384, 7, 40)])
+def test_select_splitters(accelerator, tname, np_t, direction, slots, count, picks, distinct):
+    """b200alg_select_splitters against a stable sort of the first `count` samples."""
+    op = getattr(Ops, direction + tname)
+    rng = np.random.default_rng(slots + count + picks)
+    if distinct:
+        keys = rng.integers(0, distinct, size=slots).astype(np_t)
+        if np.dtype(np_t).kind != "u":
+            keys = keys - np_t(distinct // 2)
+    elif np.dtype(np_t).kind == "f":
+        keys = rng.standard_normal(slots).astype(np_t)
+    else:
+        info = np.iinfo(np_t)
+        keys = rng.integers(info.min, info.max, size=slots, dtype=np_t, endpoint=True)
+    index = rng.integers(0, 1 << 50, size=slots, dtype=np.int64)
+    raw = {4: np.int32, 8: np.int64}[keys.dtype.itemsize]
+    eng = NativeEngine(accelerator)
+    dkeys = torch.from_numpy(keys.view(raw).copy()).cuda().view(op.dtype)
+    dindex = torch.from_numpy(index).cuda()
+    dcount = torch.tensor([count], dtype=torch.int64, device="cuda")
+    got_keys, got_index = eng.select_splitters(dkeys, dindex, dcount, op, picks)
+    torch.cuda.synchronize()
+    got_k = got_keys.view({4: torch.int32, 8: torch.int64}[keys.dtype.itemsize]).cpu().numpy()
+    got_i = got_index.cpu().numpy()
+    if count == 0:
+        assert not got_k.any() and not got_i.any()
+        return
+    ordinal = _ordinal(keys[:count], op.descending)
+    by_rank = np.argsort(ordinal, kind="stable")      # slot order breaks ties
+    want = [int(by_rank[((j + 1) * count) // (picks + 1)]) for j in range(picks)]
+    assert np.array_equal(got_k, keys.view(raw)[want])
+    assert np.array_equal(got_i, index[want])
