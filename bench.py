@@ -728,6 +728,9 @@ def run_native(args) -> None:
         e2e_note = "each step: copy-in, sort, copy-out, one after the other on one stream (the double-buffered issue was slower in this run)"
     e2e_value = world * n / (e2e_ms * 1e-3) / 1e9
 
+    phases = None
+    if world > 1:
+        phases = sort_phase_times(sharded, bufs[0], op)   # collective: every rank calls it
     secondary = None
     if world > 1 and not args.no_secondary:
         del bufs
@@ -793,6 +796,8 @@ def run_native(args) -> None:
         "clocks": clocks,
         "parity_checked": parity_checked,
     }
+    if phases is not None:
+        line["sort_phases_ms"] = dict(phases, how="rank 0, CUDA events inside one sort call, median of 5 calls outside the timed region")
     if secondary is not None:
         line["secondary"] = secondary
     if world == 1:
@@ -812,6 +817,35 @@ def run_native(args) -> None:
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def sort_phase_times(sharded, keys, op, reps: int = 5):
+    """Device time of the phases of one multi-GPU sort on this rank (the measurement hook of
+    include/b200alg_testing.h records CUDA events where the phases meet), median of `reps`
+    collective calls."""
+    import ctypes
+    import torch
+    from ilgpu_b200.algorithms import dtype_code
+    c = sharded._communicator(sort_elements=keys.numel())
+    fn = c.M.b200alg_testing_time_sort_mg
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                           ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]
+    cap = c.sort_capacity
+    out = torch.empty(cap, dtype=keys.dtype, device=keys.device)
+    count = torch.empty(1, dtype=torch.int64, device=keys.device)
+    rows = []
+    for _ in range(reps):
+        ms = (ctypes.c_float * 6)()
+        rc = fn(c.handle, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), ctypes.c_void_p(keys.data_ptr()), None,
+                keys.numel(), dtype_code(keys.dtype), 0, 1 if op.descending else 0, ctypes.c_void_p(out.data_ptr()), None, cap,
+                ctypes.c_void_p(count.data_ptr()), ms)
+        assert rc == 0, rc
+        rows.append([float(x) for x in ms])
+    names = ["splitters", "bucket_sizes", "barrier_before_exchange", "partition_and_peer_stores",
+             "barrier_after_exchange", "local_sort"]
+    med = [sorted(r[i] for r in rows)[len(rows) // 2] for i in range(6)]
+    return {k: round(v, 4) for k, v in zip(names, med)}
 
 
 def main() -> None:

@@ -382,6 +382,14 @@ static int set_identity(cudaStream_t s, int op, void *cell) {
     return B200ALG_OK;
 }
 
+// Measurement hook (b200alg_testing_time_sort_mg): events of the calling thread's next sort,
+// recorded where one phase ends and the next begins.
+constexpr int kSortPhases = 6;
+thread_local cudaEvent_t *g_phase_events = nullptr;
+static void mark_phase(int boundary, cudaStream_t s) {
+    if (g_phase_events) cudaEventRecord(g_phase_events[boundary], s);
+}
+
 template <typename K>
 static int sort_mg_typed(b200alg_comm *c, cudaStream_t s, const void *keys, const void *values, int64_t n, int key_dtype,
                          int value_bytes, int order, void *out_keys, void *out_values, int64_t out_capacity,
@@ -398,6 +406,7 @@ static int sort_mg_typed(b200alg_comm *c, cudaStream_t s, const void *keys, cons
     const int64_t total_samples = (int64_t)G * kSamplesPerRank;
 
     // 1. splitters from (key, position) samples of every shard
+    mark_phase(0, s);
     sample_kernel<K><<<8, 256, 0, s>>>((const K *)keys, n, c->rank, msg);
     B200ALG_LAUNCH_CHECK();
     B200ALG_NCCL_TRY(c, ncclAllGather(msg, all, (size_t)msg_words, ncclInt64, c->nccl, s));
@@ -411,6 +420,7 @@ static int sort_mg_typed(b200alg_comm *c, cudaStream_t s, const void *keys, cons
     if (rc != B200ALG_OK) return rc;
 
     // 2. bucket sizes of this shard, and everybody's
+    mark_phase(1, s);
     const long long base = (long long)c->rank << kRankShift;
     rc = b200alg_bucket_count(s, n ? keys : (const void *)sample_keys, n, key_dtype, order, st->splitter_keys, (const int64_t *)st->splitter_index,
                               G - 1, base, (int64_t *)st->bucket_counts, sc + c->off_partition_temp, c->partition_temp_bytes);
@@ -424,15 +434,19 @@ static int sort_mg_typed(b200alg_comm *c, cudaStream_t s, const void *keys, cons
 
     // 3. every rank is done with what the previous sort left in its receive buffer; then the
     //    partition kernel stores each bucket straight into its owner's buffer
+    mark_phase(2, s);
     rc = rank_barrier(c, s);
     if (rc != B200ALG_OK) return rc;
+    mark_phase(3, s);
     if (n > 0) {
         rc = b200alg_bucket_scatter(s, keys, values, n, key_dtype, value_bytes, order, st->splitter_keys, (const int64_t *)st->splitter_index, G - 1,
                                     base, st->key_ptrs, st->value_ptrs, sc + c->off_partition_temp, c->partition_temp_bytes);
         if (rc != B200ALG_OK) return rc;
     }
+    mark_phase(4, s);
     rc = rank_barrier(c, s);  // every rank's stores have landed
     if (rc != B200ALG_OK) return rc;
+    mark_phase(5, s);
 
     // 4. received runs lie in source-rank order; a stable sort straight out of the receive
     //    buffer finishes the job (its length is only known on the device)
@@ -444,6 +458,7 @@ static int sort_mg_typed(b200alg_comm *c, cudaStream_t s, const void *keys, cons
         if (rc != B200ALG_OK) return rc;
     }
     B200ALG_CUDA_TRY(cudaMemcpyAsync(out_count, &st->recv_count, 8, cudaMemcpyDeviceToDevice, s));
+    mark_phase(6, s);
     return B200ALG_OK;
 }
 
@@ -667,4 +682,24 @@ extern "C" int b200alg_sort_mg(b200alg_comm *c, void *stream, const void *keys, 
     case 8: return sort_mg_typed<uint64_t>(c, s, keys, values, n, key_dtype, value_bytes, order, out_keys, out_values, out_capacity, out_count);
     }
     return B200ALG_UNSUPPORTED;
+}
+
+extern "C" int b200alg_testing_time_sort_mg(b200alg_comm *c, void *stream, const void *keys, const void *values, int64_t n,
+                                            int key_dtype, int value_bytes, int order, void *out_keys, void *out_values,
+                                            int64_t out_capacity, int64_t *out_count, float *phase_ms) {
+    if (!phase_ms) return B200ALG_INVALID_ARGUMENT;
+    cudaEvent_t ev[kSortPhases + 1];
+    for (int i = 0; i <= kSortPhases; ++i) B200ALG_CUDA_TRY(cudaEventCreate(&ev[i]));
+    g_phase_events = ev;
+    const int rc = b200alg_sort_mg(c, stream, keys, values, n, key_dtype, value_bytes, order, out_keys, out_values,
+                                   out_capacity, out_count);
+    g_phase_events = nullptr;
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (rc == B200ALG_OK && e == cudaSuccess) {
+        for (int i = 0; i < kSortPhases; ++i)
+            if (cudaEventElapsedTime(&phase_ms[i], ev[i], ev[i + 1]) != cudaSuccess) phase_ms[i] = -1.f;
+    }
+    for (int i = 0; i <= kSortPhases; ++i) cudaEventDestroy(ev[i]);
+    if (rc != B200ALG_OK) return rc;
+    return e == cudaSuccess ? B200ALG_OK : B200ALG_CUDA_ERROR;
 }

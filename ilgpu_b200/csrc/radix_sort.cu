@@ -310,6 +310,45 @@ template <typename K> struct SplitterBucket {
     static __device__ __forceinline__ void *value_pointer(const unsigned char *tables, unsigned int bucket) {
         return reinterpret_cast<void *const *>(tables + kValuePointersAt)[bucket];
     }
+    // Up to SLOTS (1, 3 or 7) splitters, compared without a loop or a branch: the number of
+    // splitters with a smaller key, and whether one has the same key (then resolve_tie decides).
+    // The slots come with 16-byte loads from one address for the whole warp.
+    template <int SLOTS>
+    __device__ __forceinline__ unsigned int few(K key, const unsigned char *tables, bool &tie) const {
+        const K *sk = reinterpret_cast<const K *>(tables + kKeysAt);
+        const K tk = xf(key);
+        if constexpr (SLOTS == 1) {
+            const K only = sk[0];
+            tie = only == tk;
+            return only < tk;
+        } else {
+            constexpr int kVecs = ((SLOTS + 1) * (int)sizeof(K) + 15) / 16;
+            union { uint4 v[kVecs]; K k[kVecs * 16 / sizeof(K)]; } s;
+            const uint4 *from = reinterpret_cast<const uint4 *>(sk);
+#pragma unroll
+            for (int q = 0; q < kVecs; ++q) s.v[q] = from[q];
+            unsigned int b = 0;
+            tie = false;
+#pragma unroll
+            for (int j = 0; j < SLOTS; ++j) {
+                b += s.k[j] < tk;
+                tie |= s.k[j] == tk;
+            }
+            return b;
+        }
+    }
+    // b splitters have a smaller key than this element; walks over those with an equal key whose
+    // index does not exceed the element's.
+    // (Not inlined, and without `this`: the call sits in a branch that is almost never taken.)
+    static __device__ __noinline__ unsigned int resolve_tie(KeyXform<K> xf, int64_t index_base, int num_splitters, K key,
+                                                            int64_t local_index, const unsigned char *tables, unsigned int b) {
+        const K *sk = reinterpret_cast<const K *>(tables + kKeysAt);
+        const int64_t *si = reinterpret_cast<const int64_t *>(tables + kIndexAt);
+        const K tk = xf(key);
+        const int64_t gi = index_base + local_index;
+        while ((int)b < num_splitters && sk[b] == tk && si[b] <= gi) ++b;
+        return b;
+    }
     __device__ __forceinline__ unsigned int operator()(K key, int64_t local_index, const unsigned char *tables) const {
         const K *sk = reinterpret_cast<const K *>(tables + kKeysAt);
         const K tk = xf(key);
@@ -520,52 +559,84 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
     const unsigned int lt = lanemask_lt();
     const unsigned int my_bit = 1u << lane;
     const unsigned char *tables = smem_raw + L::off_splitters;  // of a SplitterBucket; unused otherwise
-    // A partition into up to eight buckets finds equal "digits" inside a warp by votes instead of
-    // the tables (with so few distinct values the tables serialise: all lanes of a bucket hit
-    // one word).  The buckets differ in their low three bits, the padding digit of a ragged
-    // tile from them in the fourth.  Uniform over the grid.
-    bool by_votes = false;
-    int votes = 0;
-    if constexpr (Digit::kUsesIndex) {
-        const int ns = dg.num_splitters;
-        by_votes = ns <= Digit::kSmall;
-        votes = !FAST ? 4 : (ns == 0 ? 0 : (ns == 1 ? 1 : (ns <= 3 ? 2 : 3)));
-    }
     unsigned int packed[ITEMS];  // (rank among the warp's keys of that digit) << 8 | digit
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-        unsigned int d;
-        if (FAST) {
-            d = dg(key[i], tile_base + warp_base + i * 32, tables);
-        } else {
-            const int local = warp_base + i * 32;
-            d = local < valid ? dg(key[i], tile_base + local, tables) : 0xFFu;  // padding ranks behind every real key
-        }
-        unsigned int peers;
-        if (by_votes) {
-            peers = 0xffffffffu;
-#pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                if (b < votes) {
-                    const bool bit = ((d >> b) & 1u) != 0u;
-                    const unsigned int m = __ballot_sync(0xffffffffu, bit);
-                    peers &= bit ? m : ~m;
-                }
-            }
-        } else {
-            atomicOr(&my_mask[d], my_bit);
-            __syncwarp();
-            peers = my_mask[d];
-            __syncwarp();
-        }
+    // the lowest lane of `peers` adds their number to the warp's count of digit d; everybody gets
+    // the count before and adds the peers in front of it
+    auto take_ranks = [&](int i, unsigned int d, unsigned int peers, bool clear_mask) {
         unsigned int count = 0u;
         if ((peers & lt) == 0u) {  // lowest lane with this digit
             count = atomicAdd(&my_count[d], (unsigned int)__popc(peers));
-            if (!by_votes) my_mask[d] = 0u;
+            if (clear_mask) my_mask[d] = 0u;
         }
         __syncwarp();  // the counts advance item by item
         count = __shfl_sync(0xffffffffu, count, __ffs(peers) - 1);
         packed[i] = ((count + (unsigned int)__popc(peers & lt)) << 8) | d;
+    };
+    auto rank_by_tables = [&]() {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            unsigned int d;
+            if (FAST) {
+                d = dg(key[i], tile_base + warp_base + i * 32, tables);
+            } else {
+                const int local = warp_base + i * 32;
+                d = local < valid ? dg(key[i], tile_base + local, tables) : 0xFFu;  // padding ranks behind every real key
+            }
+            atomicOr(&my_mask[d], my_bit);
+            __syncwarp();
+            const unsigned int peers = my_mask[d];
+            __syncwarp();
+            take_ranks(i, d, peers, true);
+        }
+    };
+    if constexpr (Digit::kUsesIndex) {
+        // A partition into up to eight buckets: with so few distinct "digits" the tables would
+        // serialise (all lanes of a bucket hit one word), so the lanes find their peers by warp
+        // votes on the bits the buckets differ in (and, in a ragged tile, the bit that tells the
+        // padding digit from them).  Buckets first, for all items, without a branch; an element
+        // whose key equals a splitter's (rare) is settled by its index afterwards.
+        auto rank_by_votes = [&](auto slots) {
+            constexpr int SLOTS = decltype(slots)::value;
+            constexpr int BITS = SLOTS == 1 ? 1 : (SLOTS == 3 ? 2 : 3);
+            unsigned int ties = 0u;
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+                bool tie;
+                unsigned int d = dg.template few<SLOTS>(key[i], tables, tie);
+                if (!FAST && warp_base + i * 32 >= valid) {
+                    d = 0xFFu;
+                    tie = false;
+                }
+                packed[i] = d;
+                ties |= tie ? 1u << i : 0u;
+            }
+            if (ties) {
+#pragma unroll
+                for (int i = 0; i < ITEMS; ++i)
+                    if ((ties >> i) & 1u)
+                        packed[i] = Digit::resolve_tie(dg.xf, dg.index_base, dg.num_splitters, key[i], tile_base + warp_base + i * 32,
+                                                       tables, packed[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+                const unsigned int d = packed[i];
+                unsigned int peers = 0xffffffffu;
+#pragma unroll
+                for (int b = 0; b < BITS + (FAST ? 0 : 1); ++b) {
+                    const bool bit = ((d >> (b < BITS ? b : 3)) & 1u) != 0u;
+                    const unsigned int m = __ballot_sync(0xffffffffu, bit);
+                    peers &= bit ? m : ~m;
+                }
+                take_ranks(i, d, peers, false);
+            }
+        };
+        const int ns = dg.num_splitters;  // uniform over the grid
+        if (ns <= 1) rank_by_votes(std::integral_constant<int, 1>{});
+        else if (ns <= 3) rank_by_votes(std::integral_constant<int, 3>{});
+        else if (ns <= Digit::kSmall) rank_by_votes(std::integral_constant<int, 7>{});
+        else rank_by_tables();
+    } else {
+        rank_by_tables();
     }
     __syncthreads();  // A: the tables are complete; every thread has its keys out of the staging buffer
 
@@ -714,15 +785,21 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
             const bool scattered = dg.bucket_keys != nullptr;
             for (int b = 0; b <= dg.num_splitters; ++b) {
                 const int lo = (int)bin_excl[b], hi = (int)bin_excl[b + 1];  // padding keys rank last
-                const Idx g = bin_goff[b];
-                K *kd = scattered ? reinterpret_cast<K *>(Digit::key_pointer(tables, b)) : c.dst;
-                const int64_t ks = scattered ? 1 : c.dst_stride;
-                if (keys_too)
-                    for (int p = lo + tid; p < hi; p += THREADS) kd[(int64_t)(g + (Idx)p) * ks] = skeys[p];
+                const Idx g = bin_goff[b];  // modulo 2^32 or 2^64: only g + p is an index
+                if (keys_too) {
+                    K *kd = scattered ? reinterpret_cast<K *>(Digit::key_pointer(tables, b)) : c.dst;
+                    if (scattered || FAST) {
+#pragma unroll 4
+                        for (int p = lo + tid; p < hi; p += THREADS) kd[(Idx)(g + (Idx)p)] = skeys[p];
+                    } else {
+                        for (int p = lo + tid; p < hi; p += THREADS) kd[(int64_t)(Idx)(g + (Idx)p) * c.dst_stride] = skeys[p];
+                    }
+                }
                 if constexpr (!std::is_same<V, NoValue>::value) {
                     if (values_too) {
                         V *vd = scattered && dg.bucket_values ? reinterpret_cast<V *>(Digit::value_pointer(tables, b)) : c.vdst;
-                        for (int p = lo + tid; p < hi; p += THREADS) vd[g + (Idx)p] = svals[p];
+#pragma unroll 4
+                        for (int p = lo + tid; p < hi; p += THREADS) vd[(Idx)(g + (Idx)p)] = svals[p];
                     }
                 }
             }
@@ -1090,7 +1167,14 @@ bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K>
     const int64_t step = (int64_t)gridDim.x * 256;
     const int64_t gtid = (int64_t)blockIdx.x * 256 + threadIdx.x;
 
-    if (dg.num_splitters < 8) {
+    auto count_few = [&](auto slots) {
+        constexpr int SLOTS = decltype(slots)::value;
+        auto bucket = [&](K key, int64_t index) {
+            bool tie;
+            unsigned int d = dg.template few<SLOTS>(key, tables, tie);
+            if (tie) d = SplitterBucket<K>::resolve_tie(dg.xf, dg.index_base, dg.num_splitters, key, index, tables, d);
+            return d;
+        };
         constexpr int VEC = 16 / (int)sizeof(K);
         union Pack { uint4 u; K k[VEC]; };
         int64_t head = (int64_t)(((16u - (unsigned)((uintptr_t)keys & 15u)) & 15u) / sizeof(K));
@@ -1108,14 +1192,14 @@ bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K>
             pending = 0;
         };
         int64_t v = gtid;
-        for (; v + step < nvec; v += 2 * step) {
+        for (; v + step < nvec; v += 2 * step) {  // two 16-byte loads in flight per thread (four measured slower)
             Pack a, b;
             a.u = __ldcs(vin + v);
             b.u = __ldcs(vin + v + step);
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(a.k[k], head + v * VEC + k, tables));
+            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * bucket(a.k[k], head + v * VEC + k));
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(b.k[k], head + (v + step) * VEC + k, tables));
+            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * bucket(b.k[k], head + (v + step) * VEC + k));
             pending += 2 * VEC;
             if (pending > 255 - 2 * VEC) flush();
         }
@@ -1123,16 +1207,16 @@ bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K>
             Pack a;
             a.u = __ldcs(vin + v);
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * dg(a.k[k], head + v * VEC + k, tables));
+            for (int k = 0; k < VEC; ++k) bytes += 1ull << (8 * bucket(a.k[k], head + v * VEC + k));
             pending += VEC;
             if (pending > 255 - 2 * VEC) flush();
         }
-        flush();
         if (blockIdx.x == 0) {  // the unaligned ends: fewer than 16 bytes each
-            if (threadIdx.x < head) total[dg(keys[threadIdx.x], threadIdx.x, tables)] += 1u;
+            if (threadIdx.x < head) bytes += 1ull << (8 * bucket(keys[threadIdx.x], threadIdx.x));
             const int64_t j = tail + threadIdx.x;
-            if (j < n) total[dg(keys[j], j, tables)] += 1u;
+            if (j < n) bytes += 1ull << (8 * bucket(keys[j], j));
         }
+        flush();
 #pragma unroll
         for (int b = 0; b < 8; ++b) {
             unsigned int t = total[b];
@@ -1140,7 +1224,12 @@ bucket_histogram_kernel(const K *__restrict__ keys, int64_t n, SplitterBucket<K>
             for (int d = 16; d > 0; d >>= 1) t += __shfl_down_sync(0xffffffffu, t, d);
             if ((threadIdx.x & 31) == 0 && t) mine[b] = t;
         }
-    } else {
+    };
+    const int ns = dg.num_splitters;  // uniform over the grid
+    if (ns <= 1) count_few(std::integral_constant<int, 1>{});
+    else if (ns <= 3) count_few(std::integral_constant<int, 3>{});
+    else if (ns <= SplitterBucket<K>::kSmall) count_few(std::integral_constant<int, 7>{});
+    else {
         for (int64_t i = gtid; i < n; i += step) atomicAdd(mine + dg(keys[i], i, tables), 1u);
     }
     __syncthreads();
