@@ -783,14 +783,27 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
     auto store_runs = [&](bool keys_too, bool values_too) {
         if constexpr (Digit::kUsesIndex) {
             const bool scattered = dg.bucket_keys != nullptr;
+            // A run is stored so that every warp writes whole, aligned 128-byte lines of the
+            // destination (the first lanes take the elements in front of the first line start):
+            // stores into a peer's memory are not merged on the way, a line written in two pieces
+            // crosses NVLink as two packets.
+            auto store_run = [&](auto *dest, const auto *from, int lo, int hi, Idx g) {
+                using T = std::remove_reference_t<decltype(*dest)>;
+                const Idx first = (Idx)(g + (Idx)lo);
+                const int past = (int)(((uintptr_t)(dest + first) / sizeof(T)) % 32u);  // elements past a warp-sized line start
+                int head = past ? 32 - past : 0;
+                if (head > hi - lo) head = hi - lo;
+                if (tid < head) dest[(Idx)(first + (Idx)tid)] = from[lo + tid];
+#pragma unroll 4
+                for (int p = lo + head + tid; p < hi; p += THREADS) dest[(Idx)(g + (Idx)p)] = from[p];
+            };
             for (int b = 0; b <= dg.num_splitters; ++b) {
                 const int lo = (int)bin_excl[b], hi = (int)bin_excl[b + 1];  // padding keys rank last
                 const Idx g = bin_goff[b];  // modulo 2^32 or 2^64: only g + p is an index
                 if (keys_too) {
                     K *kd = scattered ? reinterpret_cast<K *>(Digit::key_pointer(tables, b)) : c.dst;
                     if (scattered || FAST) {
-#pragma unroll 4
-                        for (int p = lo + tid; p < hi; p += THREADS) kd[(Idx)(g + (Idx)p)] = skeys[p];
+                        store_run(kd, skeys, lo, hi, g);
                     } else {
                         for (int p = lo + tid; p < hi; p += THREADS) kd[(int64_t)(Idx)(g + (Idx)p) * c.dst_stride] = skeys[p];
                     }
@@ -798,8 +811,7 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
                 if constexpr (!std::is_same<V, NoValue>::value) {
                     if (values_too) {
                         V *vd = scattered && dg.bucket_values ? reinterpret_cast<V *>(Digit::value_pointer(tables, b)) : c.vdst;
-#pragma unroll 4
-                        for (int p = lo + tid; p < hi; p += THREADS) vd[(Idx)(g + (Idx)p)] = svals[p];
+                        store_run(vd, svals, lo, hi, g);
                     }
                 }
             }
