@@ -466,6 +466,20 @@ def run_profile_case(case: str) -> None:
         for r in range(3):
             keys = synthetic.zipf_uint64_device(n, 4 + r, "cuda")
             sort(None, keys, vals.clone(), temp)
+    elif case == "partition":
+        # the partition + exchange step of the multi-GPU sort on one GPU: two buckets (split at
+        # the middle of the key range), each stored into a buffer of its own
+        from ilgpu_b200.multi_gpu import NativeEngine
+        n = 1 << 26
+        eng = NativeEngine(acc)
+        op = Sorts.AscendingUInt32
+        splitter_keys = torch.tensor([-(1 << 31)], dtype=torch.int32, device="cuda").view(torch.uint32)   # 0x80000000
+        splitter_index = torch.zeros(1, dtype=torch.int64, device="cuda")
+        halves = [torch.empty(n, dtype=torch.uint32, device="cuda") for _ in range(2)]
+        for r in range(3):
+            keys = synthetic.uniform_uint32_device(n, SEED + r, "cuda")
+            eng.bucket_count(keys, op, splitter_keys, splitter_index, 0)
+            eng.bucket_scatter(keys, None, op, splitter_keys, splitter_index, 0, [h.data_ptr() for h in halves], None)
     elif case == "scan":
         n = 1 << 28
         x = synthetic.uniform_float32_device(n, 5, "cuda")
@@ -855,7 +869,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the scan / reduce / histogram figures")
-    ap.add_argument("--profile-case", choices=["sort", "sort_pairs", "scan", "reduce", "histogram"],
+    ap.add_argument("--profile-case", choices=["sort", "sort_pairs", "partition", "scan", "reduce", "histogram"],
                     help="run a few launches of one primitive on a small case and exit (the target of ncu captures)")
     args = ap.parse_args()
     if args.warmup < 3:
