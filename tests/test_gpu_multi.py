@@ -74,6 +74,36 @@ def _worker(rank, world, port):
         np.testing.assert_array_equal(np.concatenate([p[1] for p in gathered]), zv[order])
         sizes = [len(p[0]) for p in gathered]
         assert min(sizes) > 0.5 * n / world, sizes        # duplicates are split by position: balanced
+
+        # uneven shards, one of them empty; descending signed keys with duplicates
+        dk = synthetic.uniform_int32(n, seed=7, lo=-5000, hi=5000)
+        cuts = [0, 0] + [n * r // world + 17 * r for r in range(2, world)] + [n]      # rank 0 holds nothing
+        part = dk[cuts[rank]:cuts[rank + 1]].copy()
+        uneven = ShardedAlgorithms(ib.Accelerator(rank), sort_capacity=n + 1024)      # a shard may be the whole input
+        out, m = uneven.SortKeys(dev(part), Sorts.DescendingInt32)
+        dist.all_gather_object(gathered, out.cpu().numpy())
+        np.testing.assert_array_equal(np.concatenate(gathered), np.sort(dk)[::-1])
+
+        # the measurement hook: the same sort with events where its phases meet
+        import ctypes
+        from ilgpu_b200.algorithms import dtype_code
+        c = sh._communicator(sort_elements=n)
+        fn = c.M.b200alg_testing_time_sort_mg
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                               ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]
+        mine = dev(_shard(keys, rank, world))
+        res = torch.empty(c.sort_capacity, dtype=torch.uint32, device="cuda")
+        cnt = torch.zeros(1, dtype=torch.int64, device="cuda")
+        ms = (ctypes.c_float * 6)()
+        rc = fn(c.handle, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), ctypes.c_void_p(mine.data_ptr()), None,
+                mine.numel(), dtype_code(mine.dtype), 0, 0, ctypes.c_void_p(res.data_ptr()), None, c.sort_capacity,
+                ctypes.c_void_p(cnt.data_ptr()), ms)
+        assert rc == 0, rc
+        assert all(0.0 <= x < 1000.0 for x in ms), list(ms)
+        sh.CheckStatus()
+        dist.all_gather_object(gathered, res[:int(cnt.item())].cpu().numpy())
+        np.testing.assert_array_equal(np.concatenate(gathered), np.sort(keys))
         torch.cuda.synchronize()
     finally:
         dist.destroy_process_group()
