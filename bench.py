@@ -467,19 +467,21 @@ def run_profile_case(case: str) -> None:
             keys = synthetic.zipf_uint64_device(n, 4 + r, "cuda")
             sort(None, keys, vals.clone(), temp)
     elif case == "partition":
-        # the partition + exchange step of the multi-GPU sort on one GPU: two buckets (split at
-        # the middle of the key range), each stored into a buffer of its own
+        # the partition + exchange step of the multi-GPU sort on one GPU: eight buckets (equal
+        # slices of the key range, as on an 8-GPU box), each stored into a buffer of its own
         from ilgpu_b200.multi_gpu import NativeEngine
         n = 1 << 26
         eng = NativeEngine(acc)
         op = Sorts.AscendingUInt32
-        splitter_keys = torch.tensor([-(1 << 31)], dtype=torch.int32, device="cuda").view(torch.uint32)   # 0x80000000
-        splitter_index = torch.zeros(1, dtype=torch.int64, device="cuda")
-        halves = [torch.empty(n, dtype=torch.uint32, device="cuda") for _ in range(2)]
+        cuts = [(j << 32) // 8 for j in range(1, 8)]
+        splitter_keys = torch.tensor([c - (1 << 32) if c >= (1 << 31) else c for c in cuts], dtype=torch.int32,
+                                     device="cuda").view(torch.uint32)
+        splitter_index = torch.zeros(7, dtype=torch.int64, device="cuda")
+        parts = [torch.empty(n // 8 + (1 << 20), dtype=torch.uint32, device="cuda") for _ in range(8)]
         for r in range(3):
             keys = synthetic.uniform_uint32_device(n, SEED + r, "cuda")
             eng.bucket_count(keys, op, splitter_keys, splitter_index, 0)
-            eng.bucket_scatter(keys, None, op, splitter_keys, splitter_index, 0, [h.data_ptr() for h in halves], None)
+            eng.bucket_scatter(keys, None, op, splitter_keys, splitter_index, 0, [p.data_ptr() for p in parts], None)
     elif case == "scan":
         n = 1 << 28
         x = synthetic.uniform_float32_device(n, 5, "cuda")

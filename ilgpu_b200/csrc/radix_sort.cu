@@ -310,30 +310,37 @@ template <typename K> struct SplitterBucket {
     static __device__ __forceinline__ void *value_pointer(const unsigned char *tables, unsigned int bucket) {
         return reinterpret_cast<void *const *>(tables + kValuePointersAt)[bucket];
     }
-    // Up to SLOTS (1, 3 or 7) splitters, compared without a loop or a branch: the number of
-    // splitters with a smaller key, and whether one has the same key (then resolve_tie decides).
-    // The slots come with 16-byte loads from one address for the whole warp.
+    // Up to SLOTS (1, 3 or 7) splitters, without a loop or a branch: the number of splitters with
+    // a smaller key, and whether the next one has the same key (then resolve_tie decides).  The
+    // slots come with 16-byte loads from one address for the whole warp.
     template <int SLOTS>
     __device__ __forceinline__ unsigned int few(K key, const unsigned char *tables, bool &tie) const {
         const K *sk = reinterpret_cast<const K *>(tables + kKeysAt);
         const K tk = xf(key);
+        unsigned int b;
         if constexpr (SLOTS == 1) {
             const K only = sk[0];
             tie = only == tk;
             return only < tk;
         } else {
+            // the slots ascend (unused ones hold the largest key): a search tree of selects
             constexpr int kVecs = ((SLOTS + 1) * (int)sizeof(K) + 15) / 16;
             union { uint4 v[kVecs]; K k[kVecs * 16 / sizeof(K)]; } s;
             const uint4 *from = reinterpret_cast<const uint4 *>(sk);
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) s.v[q] = from[q];
-            unsigned int b = 0;
-            tie = false;
-#pragma unroll
-            for (int j = 0; j < SLOTS; ++j) {
-                b += s.k[j] < tk;
-                tie |= s.k[j] == tk;
+            if constexpr (SLOTS == 3) {
+                const bool c1 = s.k[1] < tk;
+                const bool c2 = (c1 ? s.k[2] : s.k[0]) < tk;
+                b = (c1 ? 2u : 0u) + (c2 ? 1u : 0u);
+            } else {
+                const bool c1 = s.k[3] < tk;
+                const bool c2 = (c1 ? s.k[5] : s.k[1]) < tk;
+                const K upper = c2 ? s.k[6] : s.k[4], lower = c2 ? s.k[2] : s.k[0];
+                const bool c3 = (c1 ? upper : lower) < tk;
+                b = (c1 ? 4u : 0u) + (c2 ? 2u : 0u) + (c3 ? 1u : 0u);
             }
+            tie = sk[b] == tk;  // slot b is the first that is not smaller (slot SLOTS is padding)
             return b;
         }
     }
@@ -590,14 +597,16 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
         }
     };
     if constexpr (Digit::kUsesIndex) {
-        // A partition into up to eight buckets: with so few distinct "digits" the tables would
-        // serialise (all lanes of a bucket hit one word), so the lanes find their peers by warp
-        // votes on the bits the buckets differ in (and, in a ragged tile, the bit that tells the
-        // padding digit from them).  Buckets first, for all items, without a branch; an element
-        // whose key equals a splitter's (rare) is settled by its index afterwards.
-        auto rank_by_votes = [&](auto slots) {
+        // A partition into up to eight buckets.  Buckets first, for all items, without a branch; an
+        // element whose key equals a splitter's (rare) is settled by its index afterwards.  With
+        // two or four buckets the tables would serialise (all lanes of a bucket hit one word), so
+        // the lanes find their peers by warp votes on the bits the buckets differ in (and, in a
+        // ragged tile, the bit that tells the padding digit from them); eight buckets spread over
+        // the tables much as random digits do, and the votes would cost more issue slots.
+        auto rank_few = [&](auto slots) {
             constexpr int SLOTS = decltype(slots)::value;
-            constexpr int BITS = SLOTS == 1 ? 1 : (SLOTS == 3 ? 2 : 3);
+            constexpr int BITS = SLOTS == 1 ? 1 : 2;
+            constexpr bool VOTES = SLOTS <= 3;  // eight buckets spread over the tables like digits do
             unsigned int ties = 0u;
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
@@ -620,20 +629,28 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
                 const unsigned int d = packed[i];
-                unsigned int peers = 0xffffffffu;
+                unsigned int peers;
+                if constexpr (VOTES) {
+                    peers = 0xffffffffu;
 #pragma unroll
-                for (int b = 0; b < BITS + (FAST ? 0 : 1); ++b) {
-                    const bool bit = ((d >> (b < BITS ? b : 3)) & 1u) != 0u;
-                    const unsigned int m = __ballot_sync(0xffffffffu, bit);
-                    peers &= bit ? m : ~m;
+                    for (int b = 0; b < BITS + (FAST ? 0 : 1); ++b) {
+                        const bool bit = ((d >> (b < BITS ? b : 3)) & 1u) != 0u;
+                        const unsigned int m = __ballot_sync(0xffffffffu, bit);
+                        peers &= bit ? m : ~m;
+                    }
+                } else {
+                    atomicOr(&my_mask[d], my_bit);
+                    __syncwarp();
+                    peers = my_mask[d];
+                    __syncwarp();
                 }
-                take_ranks(i, d, peers, false);
+                take_ranks(i, d, peers, !VOTES);
             }
         };
         const int ns = dg.num_splitters;  // uniform over the grid
-        if (ns <= 1) rank_by_votes(std::integral_constant<int, 1>{});
-        else if (ns <= 3) rank_by_votes(std::integral_constant<int, 3>{});
-        else if (ns <= Digit::kSmall) rank_by_votes(std::integral_constant<int, 7>{});
+        if (ns <= 1) rank_few(std::integral_constant<int, 1>{});
+        else if (ns <= 3) rank_few(std::integral_constant<int, 3>{});
+        else if (ns <= Digit::kSmall) rank_few(std::integral_constant<int, 7>{});
         else rank_by_tables();
     } else {
         rank_by_tables();
@@ -788,14 +805,15 @@ __device__ __forceinline__ int onesweep_tile(const PassContext<K, V, SW> &c, int
             // stores into a peer's memory are not merged on the way, a line written in two pieces
             // crosses NVLink as two packets.
             auto store_run = [&](auto *dest, const auto *from, int lo, int hi, Idx g) {
-                using T = std::remove_reference_t<decltype(*dest)>;
-                const Idx first = (Idx)(g + (Idx)lo);
-                const int past = (int)(((uintptr_t)(dest + first) / sizeof(T)) % 32u);  // elements past a warp-sized line start
-                int head = past ? 32 - past : 0;
-                if (head > hi - lo) head = hi - lo;
-                if (tid < head) dest[(Idx)(first + (Idx)tid)] = from[lo + tid];
-#pragma unroll 4
-                for (int p = lo + head + tid; p < hi; p += THREADS) dest[(Idx)(g + (Idx)p)] = from[p];
+                using T = std::remove_const_t<std::remove_reference_t<decltype(*dest)>>;
+                if (hi <= lo) return;
+                T *to = dest + (Idx)(g + (Idx)lo);                             // where the run's first element goes
+                const int past = (int)(((uintptr_t)to / sizeof(T)) & 31u);     // its distance from a warp-sized line start
+                to -= past;                                                    // slot v of the run's lines: to[v] = run[v - past]
+                const T *run = from + lo - past;
+                const int end = past + (hi - lo);
+                for (int v = tid; v < end; v += THREADS)
+                    if (v >= past) to[v] = run[v];
             };
             for (int b = 0; b <= dg.num_splitters; ++b) {
                 const int lo = (int)bin_excl[b], hi = (int)bin_excl[b + 1];  // padding keys rank last
