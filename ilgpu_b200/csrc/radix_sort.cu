@@ -356,46 +356,15 @@ template <typename K> struct SplitterBucket {
         while ((int)b < num_splitters && sk[b] == tk && si[b] <= gi) ++b;
         return b;
     }
+    // Any number of splitters (the partition uses few<> for up to kSmall of them): a linear count.
     __device__ __forceinline__ unsigned int operator()(K key, int64_t local_index, const unsigned char *tables) const {
         const K *sk = reinterpret_cast<const K *>(tables + kKeysAt);
         const K tk = xf(key);
         // The splitters ascend by (key, index): count those with a smaller key, then walk over
         // the (rare) ones with an equal key whose index does not exceed this element's.
         unsigned int b = 0;
-        bool tie = false;
-        if (num_splitters <= kSmall) {
-            // eight slots, fetched with 16-byte loads from one address for the whole warp: a
-            // couple of shared-memory wavefronts per key instead of one per splitter; the
-            // branches below are uniform over the grid
-            constexpr int kVecs = (8 * (int)sizeof(K) + 15) / 16;
-            union { uint4 v[kVecs]; K k[16 / sizeof(K) > 8 ? 16 / sizeof(K) : 8]; } s;
-            const uint4 *from = reinterpret_cast<const uint4 *>(sk);
-            if (num_splitters <= 1) {
-                const K only = sk[0];
-                b = only < tk;
-                tie = only == tk;
-            } else if (num_splitters <= 3) {
-                s.v[0] = from[0];
-                if (sizeof(K) == 8) s.v[1 % kVecs] = from[1 % kVecs];
-#pragma unroll
-                for (int j = 0; j < 3; ++j) {
-                    b += s.k[j] < tk;
-                    tie |= s.k[j] == tk;
-                }
-            } else {
-#pragma unroll
-                for (int q = 0; q < kVecs; ++q) s.v[q] = from[q];
-#pragma unroll
-                for (int j = 0; j < kSmall; ++j) {
-                    b += s.k[j] < tk;
-                    tie |= s.k[j] == tk;
-                }
-            }
-        } else {
-            for (int j = 0; j < num_splitters; ++j) b += sk[j] < tk;
-            tie = (int)b < num_splitters && sk[b] == tk;
-        }
-        if (tie) {
+        for (int j = 0; j < num_splitters; ++j) b += sk[j] < tk;
+        if ((int)b < num_splitters && sk[b] == tk) {
             const int64_t *si = reinterpret_cast<const int64_t *>(tables + kIndexAt);
             const int64_t gi = index_base + local_index;
             while ((int)b < num_splitters && sk[b] == tk && si[b] <= gi) ++b;
