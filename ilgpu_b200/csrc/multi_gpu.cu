@@ -20,6 +20,15 @@ namespace b200alg {
 
 constexpr int kMaxRanks = 16;
 constexpr int kSamplesPerRank = 2048;
+// The flag allocation of a rank is mapped into every other rank.  Behind the barrier flags it
+// holds two mailboxes that the others store into directly (peer stores over NVLink, made
+// visible by the barrier that follows): the sample messages and the rows of the bucket-size
+// matrix of the sort in flight.
+constexpr int64_t kFlagBytes = 256;
+constexpr int64_t kSampleMessageWords = 2 * kSamplesPerRank + 1;
+constexpr int64_t kSampleMailboxAt = kFlagBytes;
+constexpr int64_t kMatrixMailboxAt = kSampleMailboxAt + 8ll * kMaxRanks * kSampleMessageWords;
+constexpr int64_t kMailboxEnd = kMatrixMailboxAt + 8ll * kMaxRanks * (kMaxRanks + 1);
 // Position of element i of rank r in the tie-breaking order of the sort: r * 2^40 + i.  It only
 // has to be monotone in (rank, position).
 constexpr int kRankShift = 40;
@@ -40,8 +49,7 @@ struct PeerInfo {
 struct CommState {
     TempHeader hdr;                    // hdr.wait_limit_hit: a bounded wait ran out / receive buffer too small
     long long recv_count;              // elements this rank received in the current sort
-    long long bucket_counts[kMaxRanks + 1];              // sizes of this shard's buckets, then this rank's output capacity
-    long long matrix[kMaxRanks * (kMaxRanks + 1)];       // everybody's: matrix[src * (ranks + 1) + dst]
+    long long bucket_counts[kMaxRanks + 1];              // sizes of this shard's buckets
     void *key_ptrs[kMaxRanks];         // where bucket b of this rank's shard goes
     void *value_ptrs[kMaxRanks];
     long long sample_count;            // valid samples of the current sort
@@ -68,7 +76,7 @@ struct b200alg_comm {
     void **d_peer_recv = nullptr;           // device copies of the two tables
     unsigned int **d_peer_flags = nullptr;
     unsigned char *scratch = nullptr;       // device: sample arrays, partition temp, sort temp, histogram bins
-    int64_t off_samples_send = 0, off_samples_all = 0, off_sample_keys = 0, off_sample_index = 0,
+    int64_t off_sample_keys = 0, off_sample_index = 0,
             off_partition_temp = 0, partition_temp_bytes = 0, off_sort_temp = 0, sort_temp_bytes = 0,
             off_sink = 0, off_bins = 0, scratch_bytes = 0;
 };
@@ -186,20 +194,38 @@ __global__ void add_bins_kernel(void *bins, const void *counts, int64_t num_bins
 
 // ---- sort helpers --------------------------------------------------------------------------
 // Message of one rank: [0] shard size, [1 .. 1+s) sampled keys (raw bits, zero-extended),
-// [1+s .. 1+2s) their positions in the tie-breaking order.
+// [1+s .. 1+2s) their positions in the tie-breaking order.  Stored into slot `rank` of every
+// rank's sample mailbox.
 template <typename K>
-__global__ void sample_kernel(const K *keys, int64_t n, int rank, long long *msg) {
+__global__ void sample_kernel(const K *keys, int64_t n, int rank, int ranks, unsigned int *const *peer_flags) {
     const int s = kSamplesPerRank;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < s; i += gridDim.x * blockDim.x) {
-        if (i == 0) msg[0] = n;
         long long key = 0, pos = 0;
         if (n > 0) {
             const int64_t at = ((int64_t)i * n) / s;
             key = (long long)(unsigned long long)keys[at];
             pos = ((long long)rank << kRankShift) + at;
         }
-        msg[1 + i] = key;
-        msg[1 + s + i] = pos;
+        for (int r = 0; r < ranks; ++r) {
+            long long *msg = reinterpret_cast<long long *>(reinterpret_cast<unsigned char *>(peer_flags[r]) + kSampleMailboxAt) +
+                             (int64_t)rank * kSampleMessageWords;
+            if (i == 0) msg[0] = n;
+            msg[1 + i] = key;
+            msg[1 + s + i] = pos;
+        }
+    }
+}
+
+// Row `rank` of the bucket-size matrix (this shard's bucket sizes, then this rank's output
+// capacity) into every rank's matrix mailbox.
+__global__ void publish_counts_kernel(const long long *bucket_counts, long long out_capacity, int rank, int ranks,
+                                      unsigned int *const *peer_flags) {
+    const int j = threadIdx.x;
+    if (j > ranks) return;
+    const long long v = j < ranks ? bucket_counts[j] : out_capacity;
+    for (int r = 0; r < ranks; ++r) {
+        long long *matrix = reinterpret_cast<long long *>(reinterpret_cast<unsigned char *>(peer_flags[r]) + kMatrixMailboxAt);
+        matrix[rank * (ranks + 1) + j] = v;
     }
 }
 
@@ -229,21 +255,21 @@ __global__ void collect_samples_kernel(const long long *all, int ranks, K *sampl
 // buckets start inside the owners' receive buffers, how much this rank receives, and whether
 // every receive buffer is large enough.  If one is not, every rank sends its buckets into a
 // local sink instead, receives nothing and raises the flag.
-__global__ void plan_exchange_kernel(CommState *st, void *const *peer_recv, int rank, int ranks, long long capacity,
-                                     int key_bytes, int value_bytes, void *sink) {
+__global__ void plan_exchange_kernel(CommState *st, const long long *matrix, void *const *peer_recv, int rank, int ranks,
+                                     long long capacity, int key_bytes, int value_bytes, void *sink) {
     if (threadIdx.x != 0) return;
     const int row = ranks + 1;  // bucket sizes, then the source rank's output capacity
     bool fits = true;
     for (int b = 0; b < ranks; ++b) {
         long long column = 0;
-        for (int src = 0; src < ranks; ++src) column += st->matrix[src * row + b];
-        if (column > capacity || column > st->matrix[b * row + ranks]) fits = false;
+        for (int src = 0; src < ranks; ++src) column += matrix[src * row + b];
+        if (column > capacity || column > matrix[b * row + ranks]) fits = false;
     }
     long long mine = 0;
-    for (int src = 0; src < ranks; ++src) mine += st->matrix[src * row + rank];
+    for (int src = 0; src < ranks; ++src) mine += matrix[src * row + rank];
     for (int b = 0; b < ranks; ++b) {
         long long start = 0;
-        for (int src = 0; src < rank; ++src) start += st->matrix[src * row + b];
+        for (int src = 0; src < rank; ++src) start += matrix[src * row + b];
         if (fits) {
             st->key_ptrs[b] = (unsigned char *)peer_recv[b] + start * key_bytes;
             st->value_ptrs[b] = (unsigned char *)peer_recv[b] + capacity * 8 + start * value_bytes;
@@ -255,8 +281,6 @@ __global__ void plan_exchange_kernel(CommState *st, void *const *peer_recv, int 
     st->recv_count = fits ? mine : 0;
     if (!fits) atomicExch(&st->hdr.wait_limit_hit, 1u);
 }
-
-__global__ void store_word_kernel(long long *cell, long long v) { *cell = v; }
 
 static unsigned long long host_hash() {
     char name[256] = {0};
@@ -273,18 +297,15 @@ static int finish_comm(b200alg_comm *c, int64_t sort_capacity, cudaStream_t s) {
     c->capacity = sort_capacity < 0 ? 0 : sort_capacity;
     B200ALG_CUDA_TRY(cudaMalloc((void **)&c->state, sizeof(CommState)));
     B200ALG_CUDA_TRY(cudaMemsetAsync(c->state, 0, sizeof(CommState), s));
-    B200ALG_CUDA_TRY(cudaMalloc((void **)&c->flags, 256));
-    B200ALG_CUDA_TRY(cudaMemsetAsync(c->flags, 0, 256, s));
+    B200ALG_CUDA_TRY(cudaMalloc((void **)&c->flags, (size_t)kMailboxEnd));
+    B200ALG_CUDA_TRY(cudaMemsetAsync(c->flags, 0, (size_t)kMailboxEnd, s));
     const int64_t recv_bytes = round_up(c->capacity * 16 + 256, 256);
     B200ALG_CUDA_TRY(cudaMalloc((void **)&c->recv, (size_t)recv_bytes));
 
     // scratch layout
     const int64_t total_samples = (int64_t)G * kSamplesPerRank;
-    const int64_t msg_words = 2 * kSamplesPerRank + 1;
     int64_t off = 0;
     auto take = [&](int64_t bytes) { const int64_t at = off; off += round_up(bytes, 256); return at; };
-    c->off_samples_send = take(msg_words * 8);
-    c->off_samples_all = take(G * msg_words * 8);
     c->off_sample_keys = take(total_samples * 8);
     c->off_sample_index = take(total_samples * 8);
     c->off_bins = take(1 << 20);  // local bin counts of the histogram (up to 128 Ki 8-byte bins)
@@ -398,45 +419,49 @@ static int sort_mg_typed(b200alg_comm *c, cudaStream_t s, const void *keys, cons
     const int kb = (int)sizeof(K);
     unsigned char *sc = c->scratch;
     CommState *st = c->state;
-    long long *msg = (long long *)(sc + c->off_samples_send);
-    long long *all = (long long *)(sc + c->off_samples_all);
+    // this rank's mailboxes, filled by everybody (this rank included)
+    const long long *all = (const long long *)((const unsigned char *)c->flags + kSampleMailboxAt);
+    const long long *matrix = (const long long *)((const unsigned char *)c->flags + kMatrixMailboxAt);
     K *sample_keys = (K *)(sc + c->off_sample_keys);
     long long *sample_index = (long long *)(sc + c->off_sample_index);
-    const int64_t msg_words = 2 * kSamplesPerRank + 1;
     const int64_t total_samples = (int64_t)G * kSamplesPerRank;
 
-    // 1. splitters from (key, position) samples of every shard
+    // 1. splitters from (key, position) samples of every shard: every rank stores its samples
+    //    into everybody's mailbox; after the barrier they are all there.  (Nobody still reads the
+    //    mailboxes of the sort before: a rank gets past that sort's last barrier only when all
+    //    ranks have reached it, with their reads behind them in stream order.)
     mark_phase(0, s);
-    sample_kernel<K><<<8, 256, 0, s>>>((const K *)keys, n, c->rank, msg);
+    sample_kernel<K><<<8, 256, 0, s>>>((const K *)keys, n, c->rank, G, c->d_peer_flags);
     B200ALG_LAUNCH_CHECK();
-    B200ALG_NCCL_TRY(c, ncclAllGather(msg, all, (size_t)msg_words, ncclInt64, c->nccl, s));
+    int rc = rank_barrier(c, s);
+    if (rc != B200ALG_OK) return rc;
     collect_samples_kernel<K><<<G, 256, 0, s>>>(all, G, sample_keys, sample_index, &st->sample_count);
     B200ALG_LAUNCH_CHECK();
     // blocks lie in rank order and positions ascend inside a block, so slot order breaks ties the
     // way positions would; the splitters are the pairs of ranks j * count / G, found by counting
-    int rc = b200alg_select_splitters(s, sample_keys, (const int64_t *)sample_index, total_samples,
-                                      (const int64_t *)&st->sample_count, key_dtype, order, G - 1, st->splitter_keys,
-                                      (int64_t *)st->splitter_index, sc + c->off_sort_temp, c->sort_temp_bytes);
+    rc = b200alg_select_splitters(s, sample_keys, (const int64_t *)sample_index, total_samples,
+                                  (const int64_t *)&st->sample_count, key_dtype, order, G - 1, st->splitter_keys,
+                                  (int64_t *)st->splitter_index, sc + c->off_sort_temp, c->sort_temp_bytes);
     if (rc != B200ALG_OK) return rc;
 
-    // 2. bucket sizes of this shard, and everybody's
+    // 2. bucket sizes of this shard, stored into everybody's matrix
     mark_phase(1, s);
     const long long base = (long long)c->rank << kRankShift;
     rc = b200alg_bucket_count(s, n ? keys : (const void *)sample_keys, n, key_dtype, order, st->splitter_keys, (const int64_t *)st->splitter_index,
                               G - 1, base, (int64_t *)st->bucket_counts, sc + c->off_partition_temp, c->partition_temp_bytes);
     if (rc != B200ALG_OK) return rc;
-    store_word_kernel<<<1, 1, 0, s>>>(&st->bucket_counts[G], (long long)out_capacity);
-    B200ALG_LAUNCH_CHECK();
-    B200ALG_NCCL_TRY(c, ncclAllGather(st->bucket_counts, st->matrix, (size_t)(G + 1), ncclInt64, c->nccl, s));
-    plan_exchange_kernel<<<1, 32, 0, s>>>(st, c->d_peer_recv, c->rank, G, (long long)c->capacity, kb, value_bytes,
-                                          sc + c->off_sink);
+    publish_counts_kernel<<<1, 32, 0, s>>>(st->bucket_counts, (long long)out_capacity, c->rank, G, c->d_peer_flags);
     B200ALG_LAUNCH_CHECK();
 
-    // 3. every rank is done with what the previous sort left in its receive buffer; then the
-    //    partition kernel stores each bucket straight into its owner's buffer
+    // 3. the matrix is complete and every rank is done with what the previous sort left in its
+    //    receive buffer; each rank works out where its buckets go, then the partition kernel
+    //    stores each bucket straight into its owner's buffer
     mark_phase(2, s);
     rc = rank_barrier(c, s);
     if (rc != B200ALG_OK) return rc;
+    plan_exchange_kernel<<<1, 32, 0, s>>>(st, matrix, c->d_peer_recv, c->rank, G, (long long)c->capacity, kb, value_bytes,
+                                          sc + c->off_sink);
+    B200ALG_LAUNCH_CHECK();
     mark_phase(3, s);
     if (n > 0) {
         rc = b200alg_bucket_scatter(s, keys, values, n, key_dtype, value_bytes, order, st->splitter_keys, (const int64_t *)st->splitter_index, G - 1,

@@ -11,10 +11,12 @@
  * thread, as with NCCL).  Data of rank r precedes data of rank r + 1 in every ordering
  * the primitives define.
  *
- * Exchange steps: NCCL all-reduce / all-gather of a few words on the caller's stream; the
- * sort moves its buckets with plain stores from the partition kernel into the owner's
- * receive buffer (peer memory over NVLink; no TMA, no multicast).  Waits between GPUs are
- * NCCL's or bounded polls that end in B200ALG_WAIT_LIMIT (b200alg_comm_status).
+ * Exchange steps: reduce, histogram and scan use an NCCL all-reduce / all-gather of a few
+ * words on the caller's stream.  The sort exchanges everything with plain stores into peer
+ * memory over NVLink (no TMA, no multicast) between barriers of the library's own: its
+ * samples and bucket sizes go into mailboxes that every rank maps, its buckets from the
+ * partition kernel straight into the owner's receive buffer.  Waits between GPUs are NCCL's
+ * or bounded polls that end in B200ALG_WAIT_LIMIT (b200alg_comm_status).
  */
 #ifndef B200ALG_MG_H
 #define B200ALG_MG_H
