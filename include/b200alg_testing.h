@@ -29,8 +29,9 @@ int b200alg_testing_time_sort_pass(void *stream, void *keys, int64_t n, int key_
 /* Exported by libb200alg_mg.so.  b200alg_sort_mg (include/b200alg_mg.h: same arguments, comm is a
  * b200alg_comm*, collective over the ranks) with CUDA events where its phases meet; synchronises
  * the stream and returns the device time of this rank's six phases in phase_ms[0..6): splitters
- * (sampling, all-gather, selection), bucket sizes (count, all-gather, plan), first barrier,
- * partition with peer stores, second barrier (the wait for the slowest sender), local sort. */
+ * (samples into the mailboxes, barrier, selection), bucket sizes (count, row into the
+ * mailboxes), barrier and the plan of the exchange, partition with peer stores, last barrier
+ * (the wait for the slowest sender), local sort. */
 int b200alg_testing_time_sort_mg(void *comm, void *stream, const void *keys, const void *values, int64_t n,
                                  int key_dtype, int value_bytes, int order, void *out_keys, void *out_values,
                                  int64_t out_capacity, int64_t *out_count, float *phase_ms);
