@@ -538,7 +538,7 @@ class ShardedAlgorithms:
         (bucket histogram, offsets, count export, one pass)."""
         passes = operation.dtype.itemsize
         if self._native():
-            # samples, collect, rank + pick of the splitters, plan, capacity word, 2 barriers; the
-            # final sort (histogram, offsets, passes, copy-back); bucket sizes (3) and the partition (2)
-            return 8 + (3 + passes) + 5
+            # samples, collect, rank + pick of the splitters, row of the size matrix, plan, 3 barriers;
+            # the final sort (histogram, offsets, passes, copy-back); bucket sizes (3) and the partition (2)
+            return 9 + (3 + passes) + 5
         return 2 * (3 + passes) + 4
